@@ -1,0 +1,194 @@
+/*
+ * libmagi_attn.so - C ABI of the B200 (sm_100a) chunk-wise block-causal GQA attention core.
+ *
+ * Every entry point replaces a piece of MAGI-1's DiT self-attention (paths below are relative to the
+ * MAGI-1 project root).  Rules shared by all functions:
+ *   - plain pointers and sizes only; device pointers are raw CUDA device addresses, `stream` is a cudaStream_t
+ *     passed as void* (NULL = legacy default stream); all work is stream-ordered, nothing synchronises unless
+ *     the function says so;
+ *   - return value: 0 (MAGI_OK) or a negative MAGI_E_* code; never throws, never aborts, never computes on the
+ *     CPU.  magi_last_error() gives the text of the last failure recorded on a context;
+ *   - head_dim is fixed at 128 (the only value MAGI-1 ships: kv_channels = 128);
+ *   - one context per (device, stream in flight): contexts own a small device workspace that calls share.
+ */
+#ifndef MAGI_ATTN_H_
+#define MAGI_ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MAGI_HEAD_DIM 128
+#if defined(__GNUC__)
+#define MAGI_API __attribute__((visibility("default")))
+#else
+#define MAGI_API
+#endif
+
+enum {
+  MAGI_OK = 0,
+  MAGI_E_BADARG = -1,   /* null pointer, non-positive size, unsupported combination            */
+  MAGI_E_ALIGN = -2,    /* pointer not 16-byte aligned or stride not a multiple of 8 elements  */
+  MAGI_E_ARCH = -3,     /* device is not compute capability 10.x                               */
+  MAGI_E_RANGE = -4,    /* range / page bookkeeping inconsistent (caught on host or on device) */
+  MAGI_E_NOMEM = -5,    /* cudaMalloc failed or a fixed capacity was exceeded                  */
+  MAGI_E_NCCL = -6,     /* NCCL call failed                                                    */
+  MAGI_E_TIMEOUT = -7,  /* a bounded device-side wait gave up (reported by magi_ctx_status)    */
+  MAGI_E_CUDA = -8      /* a CUDA runtime / driver call failed                                 */
+};
+
+enum { MAGI_DTYPE_BF16 = 0, MAGI_DTYPE_FP8_E4M3 = 1 };
+enum { MAGI_NORM_LAYERNORM_1P = 0, MAGI_NORM_RMSNORM_1P = 1 };
+
+typedef struct magi_ctx magi_ctx;
+typedef struct magi_kv_cache magi_kv_cache;
+typedef struct magi_ulysses magi_ulysses;
+
+/* Library version (major*10000 + minor*100 + patch).  No counterpart in the reference. */
+MAGI_API int magi_version(void);
+/* Text for a MAGI_E_* code.  Replaces the Python asserts / exceptions the reference raises on this path. */
+MAGI_API const char* magi_strerror(int code);
+
+/* One context per GPU worker; mirrors "one Python process per GPU" of the reference launcher
+ * (example/24B/run.sh:27-38).  Allocates the plan workspace (1 MiB) on `device`.  Fails with MAGI_E_ARCH on
+ * anything but sm_100. */
+MAGI_API int magi_ctx_create(int device, magi_ctx** out);
+MAGI_API int magi_ctx_destroy(magi_ctx* ctx);
+MAGI_API const char* magi_last_error(const magi_ctx* ctx);
+/* Synchronises `stream`, then reads the device status word: 0, MAGI_E_RANGE (plan kernel met an
+ * inconsistent range) or MAGI_E_TIMEOUT (a bounded mbarrier wait in a kernel gave up).  Clears the word. */
+MAGI_API int magi_ctx_status(magi_ctx* ctx, void* stream, int* device_status);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Prologue: per-head norm + 3D RoPE, fused.  Replaces FullyParallelAttention.get_q / get_k
+ * (inference/model/dit/dit_module.py:953-963, :970-980) after the linear projection:
+ * fp32 upcast, FusedLayerNorm with weight gamma+1 (:355-357), non-interleaved rotary on the first
+ * 2*rot_pairs channels (:961), cast to bf16, and the "(sq b) hn hd" re-layout - one pass over HBM.
+ * The destination is generic enough to be (a) the packed tensor, (b) the Ulysses send buffer
+ * "seq (cp hn) hd -> (cp seq) hn hd" (inference/infra/parallelism/context_parallel.py:396) or (c) a KV-cache
+ * page: head h goes to block h / heads_per_block, head slot h % heads_per_block.
+ */
+typedef struct {
+  uint32_t struct_size;      /* sizeof(magi_prologue_params) */
+  int32_t norm_mode;         /* MAGI_NORM_*                                                        */
+  const void* x;             /* bf16 [T, H, 128] view: element (t,h,d) at x + t*x_stride_t + h*x_stride_h + d */
+  int64_t x_stride_t, x_stride_h;
+  int32_t T, H;
+  const float* gamma;        /* fp32 [128]; applied as gamma + 1                                   */
+  const float* beta;         /* fp32 [128] or NULL; ignored for RMSNORM                            */
+  float eps;
+  int32_t rot_pairs;         /* <= 64, multiple of 4; the reference uses 48.  0 = no rotary        */
+  const float* cos;          /* fp32 [T, rot_pairs]                                                */
+  const float* sin;
+  void* out;                 /* bf16; element (t,h,d) at out + (h / heads_per_block)*out_stride_block
+                                + t*out_stride_t + (h % heads_per_block)*out_stride_h + d         */
+  int64_t out_stride_t, out_stride_h, out_stride_block;
+  int32_t heads_per_block;   /* 0 or >= H: no blocking */
+  int32_t reserved;
+} magi_prologue_params;
+MAGI_API int magi_qk_norm_rope_fwd(magi_ctx* ctx, const magi_prologue_params* p, void* stream);
+
+/* Strided copy with the same destination addressing as the prologue (used for V, which has no norm/rope:
+ * FullyParallelAttention.get_v, inference/model/dit/dit_module.py:987-989, and the torch.cat of K and V at
+ * :996).  x, out: bf16. */
+MAGI_API int magi_head_block_copy(magi_ctx* ctx, const magi_prologue_params* p, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Chunk-paged KV cache.  Replaces Attention._allocate_key_and_value_memory
+ * (inference/model/dit/dit_module.py:800-819) and _full_adjust_key_and_value (:891-931): instead of one flat
+ * [max_seq, Hkv, 2*128] buffer per layer that is sliced, written and torch.cat'ed with the current K|V on
+ * every call, clean chunks live in fixed pages (one page = one chunk of one layer, K and V separate) that
+ * the attention kernel reads in place through a page list.  The cache is head-sharded under context
+ * parallelism exactly like the reference's (num_query_groups_per_partition, :794-798): create it with the
+ * local number of KV heads.
+ */
+typedef struct {
+  uint32_t struct_size;
+  int32_t dtype;            /* MAGI_DTYPE_BF16 or MAGI_DTYPE_FP8_E4M3 (per-(head,128-token block) fp32 scales) */
+  int32_t n_layers;
+  int32_t max_chunks;       /* pages per layer                                                   */
+  int32_t chunk_tokens;     /* tokens of a full chunk (e.g. 9360, 21600)                         */
+  int32_t n_kv_heads;       /* local KV heads                                                    */
+} magi_kv_cache_desc;
+MAGI_API int magi_kv_cache_create(magi_ctx* ctx, const magi_kv_cache_desc* d, magi_kv_cache** out);
+MAGI_API int magi_kv_cache_destroy(magi_kv_cache* c);
+/* Writes tokens [token_offset, token_offset + n_tokens) of chunk `chunk_id` in `layer` from bf16 K and V
+ * views [n_tokens, Hkv, 128] (strides in elements).  The page is allocated on first use of a chunk id.
+ * FP8 caches quantise here; token_offset must then be a multiple of 128.  Counterpart of the cache write
+ * at inference/model/dit/dit_module.py:918-929. */
+MAGI_API int magi_kv_cache_append(magi_kv_cache* c, int layer, int chunk_id, const void* k, int64_t k_stride_t,
+                         int64_t k_stride_h, const void* v, int64_t v_stride_t, int64_t v_stride_h, int n_tokens,
+                         int token_offset, void* stream);
+/* Frees the pages of a chunk in every layer (the reference never frees; its windows
+ * - inference/pipeline/video_generate.py:467-508 - make old chunks dead). */
+MAGI_API int magi_kv_cache_evict(magi_kv_cache* c, int chunk_id);
+/* Copies a page back out as bf16 [n_tokens, Hkv, 128] (dequantising an FP8 page); for tests and for callers
+ * that want the reference's materialised prefix (inference/model/dit/dit_module.py:914-915). */
+MAGI_API int magi_kv_cache_read(magi_kv_cache* c, int layer, int chunk_id, void* k_out, void* v_out, int n_tokens,
+                       int token_offset, void* stream);
+/* Bytes of device memory the cache holds. */
+MAGI_API int64_t magi_kv_cache_bytes(const magi_kv_cache* c);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Core attention.  Replaces the module-level `flex_attention` call in FullyParallelAttention.core_attention
+ * (inference/model/dit/dit_module.py:1032-1043; same packed varlen surface: q_ranges / k_ranges int32 [n,2] on
+ * the device, max_seqlen_q / max_seqlen_k, softmax_scale) and the per-range flash_attn_func loop (:1049-1065):
+ * for every q-range i, out[q_i] = softmax(Q[q_i] K[k_i]^T * scale) V[k_i], non-causal inside the rectangle,
+ * GQA head h -> h / (Hq/Hkv).  Rows of q covered by no range are not written.
+ *
+ * Key/value address space ("virtual" tokens) that k_ranges index, as in the reference's
+ * torch.cat([cache[:slice_point*C], current]) (:931):
+ *     [ prefix chunk 0 | prefix chunk 1 | ... | prefix chunk P-1 | current k/v tokens ]
+ * each prefix chunk being exactly cache->chunk_tokens tokens read in place from its page.
+ * Extension over the reference: with k_range_offsets a q-range may own several k intervals (their union is
+ * attended), which expresses "own cached prefix + own chunk" for concurrently denoising chunks.
+ */
+typedef struct {
+  uint32_t struct_size;
+  int32_t dtype;                 /* MAGI_DTYPE_BF16; MAGI_DTYPE_FP8_E4M3 with the *_scale fields        */
+  const void* q;                 /* [total_q, Hq, 128]; strides in elements                              */
+  int64_t q_stride_t, q_stride_h;
+  const void* k;                 /* current K [total_k, Hkv, 128] (may be NULL if total_k == 0)          */
+  int64_t k_stride_t, k_stride_h;
+  const void* v;                 /* current V [total_k, Hkv, 128]                                        */
+  int64_t v_stride_t, v_stride_h;
+  void* out;                     /* bf16 [total_q, Hq, 128]                                              */
+  int64_t o_stride_t, o_stride_h;
+  float* lse;                    /* fp32 [total_q, Hq] natural-log-sum-exp, or NULL                      */
+  int32_t total_q, total_k;
+  int32_t n_q_heads, n_kv_heads;
+  const int32_t* q_ranges;       /* device int32 [n_ranges, 2]                                           */
+  const int32_t* k_ranges;       /* device int32 [n_k_ranges, 2], virtual token coordinates              */
+  const int32_t* k_range_offsets;/* device int32 [n_ranges+1] or NULL (then n_k_ranges == n_ranges, 1:1) */
+  int32_t n_ranges, n_k_ranges;
+  int32_t max_seqlen_q;          /* upper bound of q-range lengths (sizes the grid; no host sync needed)  */
+  int32_t max_seqlen_k;          /* accepted for surface parity; unused                                  */
+  float softmax_scale;           /* <= 0: 1/sqrt(128), the reference's softmax_scale=None                */
+  const magi_kv_cache* cache;    /* NULL: no prefix                                                      */
+  int32_t layer;
+  int32_t n_prefix_chunks;       /* P <= 64                                                              */
+  const int32_t* prefix_chunk_ids; /* HOST int32 [P]                                                     */
+  /* FP8 only: fp32 scales [n_blocks, heads]; 128-token blocks counted from each multiple of scale_chunk_tokens */
+  const float* q_scale;
+  const float* k_scale;
+  const float* v_scale;
+  int32_t scale_chunk_tokens;
+  int32_t reserved;
+} magi_attn_params;
+MAGI_API int magi_chunk_attn_fwd(magi_ctx* ctx, const magi_attn_params* p, void* stream);
+/* Diagnostic twin: same plan, same arguments (bf16 only), plain CUDA-core arithmetic in fp32.  It exists so a
+ * numerical failure can be attributed to the plan or to the tensor-core kernel; it is not a dispatch target. */
+MAGI_API int magi_chunk_attn_fwd_simt(magi_ctx* ctx, const magi_attn_params* p, void* stream);
+
+/* bf16 [T,H,128] -> e4m3 [T,H,128] + fp32 scales [n_blocks,H] (scale = absmax/448 per (128-token block, head),
+ * blocks counted from each multiple of chunk_tokens).  No reference counterpart: the reference's attention is
+ * never FP8 (its fp8 path is the linear layers, inference/model/dit/dit_module.py:431-487). */
+MAGI_API int magi_quantize_e4m3_block128(magi_ctx* ctx, const void* x, int64_t stride_t, int64_t stride_h, int T, int H,
+                                int chunk_tokens, void* x8, float* scales, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MAGI_ATTN_H_ */

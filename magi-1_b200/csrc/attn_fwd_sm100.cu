@@ -1,0 +1,430 @@
+// Chunk-causal GQA attention forward for sm_100a: TMA-fed shared-memory tiles, tcgen05 UMMA with TMEM
+// accumulators, warp-level online softmax.  Replaces the flex_attention / flash_attn_func dispatch of
+// FullyParallelAttention.core_attention (inference/model/dit/dit_module.py:1023-1066).
+//
+// One CTA = one work item of the plan (up to 256 q rows of one range, one q head) and walks every K/V tile
+// of the range's segments; tiles that the block mask excludes are never in the list.
+//
+//   warp 0      TMA producer: Q tiles once, then K_j, V_j into a ring of 32 KB stages
+//   warp 1      UMMA issuer (one thread): S_x = Q_x K_j^T, O_x += P_x V_j for the two Q tiles x = 0,1
+//   warps 4-7   softmax for Q tile 0   } thread t of a warpgroup owns row t: TMEM lane = row, so row max /
+//   warps 8-11  softmax for Q tile 1   } row sum need no shuffles.  They also rescale O and store the output.
+//
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512), fp32.  P (bf16) overwrites the first
+// 64 columns of its S and is the A operand of the PV UMMA straight from TMEM.
+// While warpgroup 0 does softmax on S0 the tensor pipe runs the UMMAs of tile 1, and vice versa.
+#include <cuda_bf16.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace magi {
+using namespace ptx;
+
+constexpr int kAttnThreads = 384;
+constexpr int kTileBytes = kTileN * kHeadDim * 2;  // 32768: one 128x128 bf16 tile
+constexpr int kHalfBytes = kTileBytes / 2;         // a [128 x 64] half tile = one 128-byte-swizzled TMA box
+constexpr uint32_t kSw128 = 2;
+
+struct AttnKernelParams {
+  const void* plan;
+  __nv_bfloat16* out;
+  int64_t o_stride_t, o_stride_h;
+  float* lse;
+  int n_q_heads;
+  int group;          // q heads per kv head
+  float scale;        // softmax scale
+  float scale_log2;   // scale * log2(e)
+};
+
+template <bool kPInTmem>
+struct SmemLayout {
+  static constexpr int kStages = kPInTmem ? 4 : 3;
+  static constexpr int kQ = 0;
+  static constexpr int kRing = kQ + kTilesPerCta * kTileBytes;
+  static constexpr int kP = kRing + kStages * kTileBytes;
+  static constexpr int kBar = kP + (kPInTmem ? 0 : kTilesPerCta * kTileBytes);
+  // barriers: q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2]
+  static constexpr int kNumBars = 1 + 2 * kStages + 6;
+  static constexpr int kMisc = kBar + kNumBars * 8;
+  static constexpr int kTotal = kMisc + 16;
+  static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024 bytes
+};
+
+// K-major operand tile [128 rows x 128 k], stored as two [128 x 64] halves, 128-byte swizzle:
+// descriptor of the 16-element k-slice `k` (0..7).
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile_saddr, int k) {
+  return umma_smem_desc(tile_saddr + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024, kSw128);
+}
+// MN-major operand tile (V: [128 tokens x 128 d] as two [128 x 64] halves): k-slice = 16 tokens.
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile_saddr, int k) {
+  return umma_smem_desc(tile_saddr + k * 2048, kHalfBytes, 1024, kSw128);
+}
+
+template <bool kPInTmem>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
+                const __grid_constant__ CUtensorMap tm_vc, const AttnKernelParams p) {
+  using L = SmemLayout<kPInTmem>;
+  constexpr int kStages = L::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  PlanView pv = plan_view(const_cast<void*>(p.plan));
+  // a planner error or an earlier CTA's timeout stops the whole grid
+  if ((int)blockIdx.x >= pv.hdr->n_items || pv.hdr->status != 0) return;
+  const WorkItem it = pv.items[blockIdx.x];
+  const int head = blockIdx.y;
+  const int kv_head = head / p.group;
+  const int n_tiles = it.n_tiles;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (n_tiles == 0) {  // a q-range with no keys: define the output as zeros, lse = -inf
+    for (int idx = threadIdx.x; idx < it.q_rows * (kHeadDim / 8); idx += blockDim.x) {
+      const int r = idx / (kHeadDim / 8), c = idx % (kHeadDim / 8);
+      *reinterpret_cast<uint4*>(p.out + (int64_t)(it.q_row0 + r) * p.o_stride_t + (int64_t)head * p.o_stride_h + c * 8) =
+          make_uint4(0, 0, 0, 0);
+    }
+    if (p.lse)
+      for (int r = threadIdx.x; r < it.q_rows; r += blockDim.x)
+        p.lse[(int64_t)(it.q_row0 + r) * p.n_q_heads + head] = -INFINITY;
+    return;
+  }
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = kv_full + kStages;
+  uint64_t* s_full = kv_empty + kStages;
+  uint64_t* p_full = s_full + 2;
+  uint64_t* o_full = p_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(&s_full[x], 1);
+      mbar_init(&p_full[x], 128);
+      mbar_init(&o_full[x], 1);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  uint8_t* sQ = smem + L::kQ;
+  uint8_t* ring = smem + L::kRing;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_expect_tx(q_full, kTilesPerCta * kTileBytes);
+      for (int x = 0; x < kTilesPerCta; ++x)
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(sQ + x * kTileBytes + h * kHalfBytes, &tm_q, q_full, h * 64, head, it.q_row0 + x * kTileM);
+      int fill = 0;
+      bool ok = true;
+      for (int sg_i = it.seg_begin; sg_i < it.seg_end && ok; ++sg_i) {
+        const Segment sg = pv.segs[sg_i];
+        const CUtensorMap* mk = sg.src ? &tm_kc : &tm_k;
+        const CUtensorMap* mv = sg.src ? &tm_vc : &tm_v;
+        for (int t0 = 0; t0 < sg.len && ok; t0 += kTileN) {
+          for (int kv = 0; kv < 2; ++kv, ++fill) {
+            const int stage = fill % kStages;
+            const int use = fill / kStages;
+            if (use > 0) ok = mbar_wait(&kv_empty[stage], (use & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            mbar_expect_tx(&kv_full[stage], kTileBytes);
+            const CUtensorMap* m = kv ? mv : mk;
+            tma_load_3d(ring + stage * kTileBytes, m, &kv_full[stage], 0, kv_head, sg.row0 + t0);
+            tma_load_3d(ring + stage * kTileBytes + kHalfBytes, m, &kv_full[stage], 64, kv_head, sg.row0 + t0);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc(kTileM, kTileN, 1, 1, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc(kTileM, kHeadDim, 1, 1, 0, 1);
+      const uint32_t sQ_addr = smem_u32(sQ), ring_addr = smem_u32(ring);
+      const uint32_t sP_addr = smem_u32(smem + L::kP);
+      auto stage_of = [&](int fill) { return fill % kStages; };
+      auto parity_of = [&](int fill) { return (uint32_t)((fill / kStages) & 1); };
+      auto issue_qk = [&](int x, int j) {
+        const uint32_t a = sQ_addr + x * kTileBytes, b = ring_addr + stage_of(2 * j) * kTileBytes;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss_f16(tmem_base + x * kTileN, kmajor_desc(a, k), kmajor_desc(b, k), idesc_qk, k > 0);
+      };
+      auto issue_pv = [&](int x, int j) {
+        const uint32_t b = ring_addr + stage_of(2 * j + 1) * kTileBytes;
+        const uint32_t d = tmem_base + 2 * kTileN + x * kHeadDim;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if constexpr (kPInTmem)
+            umma_ts_f16(d, tmem_base + x * kTileN + k * 8, mnmajor_desc(b, k), idesc_pv, (j > 0) || (k > 0));
+          else
+            umma_ss_f16(d, kmajor_desc(sP_addr + x * kTileBytes, k), mnmajor_desc(b, k), idesc_pv, (j > 0) || (k > 0));
+        }
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      ok = ok && mbar_wait(&kv_full[stage_of(0)], parity_of(0), abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_qk(0, 0);
+        umma_commit(&s_full[0]);
+        issue_qk(1, 0);
+        umma_commit(&s_full[1]);
+        umma_commit(&kv_empty[stage_of(0)]);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const bool more = j + 1 < n_tiles;
+        ok = mbar_wait(&kv_full[stage_of(2 * j + 1)], parity_of(2 * j + 1), abort_flag);
+        if (ok && more) ok = mbar_wait(&kv_full[stage_of(2 * j + 2)], parity_of(2 * j + 2), abort_flag);
+        for (int x = 0; x < 2 && ok; ++x) {
+          ok = mbar_wait(&p_full[x], j & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_pv(x, j);
+          umma_commit(&o_full[x]);
+          if (x == 1) umma_commit(&kv_empty[stage_of(2 * j + 1)]);
+          if (more) {
+            issue_qk(x, j + 1);
+            umma_commit(&s_full[x]);
+            if (x == 1) umma_commit(&kv_empty[stage_of(2 * j + 2)]);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ softmax / correction / epilogue
+    const int x = (warp - 4) >> 2;          // Q tile of this warpgroup
+    const int quarter = warp & 3;           // TMEM lane quarter this warp may touch
+    const int row = quarter * 32 + lane;    // row inside the Q tile
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + x * kTileN;
+    const uint32_t tO = tmem_base + lane_base + 2 * kTileN + x * kHeadDim;
+    const float sl2 = p.scale_log2;
+    float m_used = -INFINITY;  // reference maximum currently baked into O and l (raw score units)
+    float l = 0.f;
+    int j = 0;
+    bool ok = true;
+    for (int sg_i = it.seg_begin; sg_i < it.seg_end && ok; ++sg_i) {
+      const Segment sg = pv.segs[sg_i];
+      for (int t0 = 0; t0 < sg.len && ok; t0 += kTileN, ++j) {
+        const int valid = min(kTileN, sg.len - t0);
+        ok = mbar_wait(&s_full[x], j & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        uint32_t s[kTileN];
+        tmem_ld32(tS, s);
+        tmem_ld32(tS + 32, s + 32);
+        tmem_ld32(tS + 64, s + 64);
+        tmem_ld32(tS + 96, s + 96);
+        tmem_wait_ld();
+        if (valid < kTileN) {
+#pragma unroll
+          for (int c = 0; c < kTileN; ++c)
+            if (c >= valid) s[c] = 0xff800000u;  // -inf
+        }
+        float mx = __uint_as_float(s[0]);
+#pragma unroll
+        for (int c = 1; c < kTileN; ++c) mx = fmaxf(mx, __uint_as_float(s[c]));
+        // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8 larger.
+        const float m_new = fmaxf(m_used, mx);
+        const bool need = (m_new - m_used) * sl2 > 8.0f;
+        const float m_cur = need ? m_new : m_used;
+        const float alpha = need ? ex2((m_used - m_new) * sl2) : 1.0f;
+        const float neg_m = -m_cur * sl2;
+        float rowsum0 = 0.f, rowsum1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < kTileN; c += 2) {
+          const float p0 = ex2(fmaf(__uint_as_float(s[c]), sl2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), sl2, neg_m));
+          rowsum0 += p0;
+          rowsum1 += p1;
+          s[c >> 1] = pack_bf16x2(p0, p1);
+        }
+        if constexpr (kPInTmem) {
+          tmem_st32(tS, s);
+          tmem_st32(tS + 32, s + 32);
+        } else {
+          uint8_t* sP = smem + L::kP + x * kTileBytes;
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {  // 16-byte chunk c holds columns 8c..8c+7
+            const int h = c >> 3, cc = c & 7;
+            *reinterpret_cast<uint4*>(sP + h * kHalfBytes + row * 128 + ((cc ^ (row & 7)) << 4)) =
+                make_uint4(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3]);
+          }
+        }
+        if (j > 0) {
+          // O_x of tile j-1 must be complete before it is rescaled and before P_j may be consumed.
+          ok = mbar_wait(&o_full[x], (j - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          if (__any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; ++c4) {
+              uint32_t o[32];
+              tmem_ld32(tO + c4 * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+              tmem_st32(tO + c4 * 32, o);
+            }
+          }
+        }
+        l = l * alpha + (rowsum0 + rowsum1);
+        m_used = m_cur;
+        tmem_wait_st();
+        if constexpr (!kPInTmem) fence_proxy_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(&p_full[x]);
+      }
+    }
+    if (ok) ok = mbar_wait(&o_full[x], (n_tiles - 1) & 1, abort_flag);
+    if (ok) {
+      tc_fence_after_sync();
+      const int r_in_item = x * kTileM + row;
+      const bool valid_row = r_in_item < it.q_rows;
+      const float inv = 1.0f / l;
+      __nv_bfloat16* dst = p.out + (int64_t)(it.q_row0 + r_in_item) * p.o_stride_t + (int64_t)head * p.o_stride_h;
+#pragma unroll 1
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t o[32];
+        tmem_ld32(tO + c4 * 32, o);
+        tmem_wait_ld();
+        if (valid_row) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(o[8 * c + 0]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
+            v.y = pack_bf16x2(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
+            v.z = pack_bf16x2(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
+            v.w = pack_bf16x2(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c4 * 32 + c * 8) = v;
+          }
+        }
+      }
+      if (p.lse && valid_row)
+        p.lse[(int64_t)(it.q_row0 + r_in_item) * p.n_q_heads + head] = m_used * p.scale + logf(l);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) pv.hdr->status = MAGI_E_TIMEOUT;
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// [tokens, heads, 128] view -> 3-D map (d, head, token), box = 64 x 1 x 128 rows, 128-byte swizzle.
+int make_tile_map(magi_ctx* ctx, CUtensorMap* m, const void* base, int64_t stride_t, int64_t stride_h, int tokens,
+                  int heads, int elem_bytes, const char* what) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return set_err(ctx, MAGI_E_CUDA, "cuTensorMapEncodeTiled entry point not found");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((stride_t * elem_bytes) & 15) || ((stride_h * elem_bytes) & 15))
+    return set_err(ctx, MAGI_E_ALIGN, "%s: base must be 16-byte aligned and strides multiples of 16 bytes", what);
+  cuuint64_t dims[3] = {(cuuint64_t)kHeadDim, (cuuint64_t)heads, (cuuint64_t)tokens};
+  cuuint64_t strides[2] = {(cuuint64_t)(stride_h * elem_bytes), (cuuint64_t)(stride_t * elem_bytes)};
+  cuuint32_t box[3] = {(cuuint32_t)(128 / elem_bytes), 1, (cuuint32_t)kTileN};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_err(ctx, MAGI_E_CUDA, "%s: cuTensorMapEncodeTiled failed (%d)", what, (int)r);
+  return MAGI_OK;
+}
+
+// Opt in to > 48 KB of dynamic shared memory; called once per context with its device current.
+int attn_init_device(magi_ctx* ctx) {
+  MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SmemLayout<true>::kDynamic));
+  MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SmemLayout<false>::kDynamic));
+  return MAGI_OK;
+}
+
+int launch_attn_bf16(magi_ctx* ctx, const magi_attn_params* p, int max_items, bool p_in_tmem, cudaStream_t stream) {
+  CUtensorMap tq, tk, tv, tkc, tvc;
+  int rc;
+  if ((rc = make_tile_map(ctx, &tq, p->q, p->q_stride_t, p->q_stride_h, p->total_q, p->n_q_heads, 2, "q"))) return rc;
+  const bool has_new = p->total_k > 0;
+  const bool has_cache = p->cache && p->n_prefix_chunks > 0;
+  if (has_new) {
+    if ((rc = make_tile_map(ctx, &tk, p->k, p->k_stride_t, p->k_stride_h, p->total_k, p->n_kv_heads, 2, "k"))) return rc;
+    if ((rc = make_tile_map(ctx, &tv, p->v, p->v_stride_t, p->v_stride_h, p->total_k, p->n_kv_heads, 2, "v"))) return rc;
+  }
+  if (has_cache) {
+    const magi_kv_cache* c = p->cache;
+    const int64_t st = (int64_t)c->d.n_kv_heads * kHeadDim;
+    const int rows = c->n_slots * c->page_cap;
+    if ((rc = make_tile_map(ctx, &tkc, c->k_pool, st, kHeadDim, rows, c->d.n_kv_heads, 2, "k cache"))) return rc;
+    if ((rc = make_tile_map(ctx, &tvc, c->v_pool, st, kHeadDim, rows, c->d.n_kv_heads, 2, "v cache"))) return rc;
+  }
+  if (!has_new && !has_cache) return set_err(ctx, MAGI_E_BADARG, "no keys: total_k == 0 and no prefix");
+  if (!has_new) { tk = tkc; tv = tvc; }
+  if (!has_cache) { tkc = tk; tvc = tv; }
+
+  AttnKernelParams kp;
+  kp.plan = ctx->workspace;
+  kp.out = reinterpret_cast<__nv_bfloat16*>(p->out);
+  kp.o_stride_t = p->o_stride_t;
+  kp.o_stride_h = p->o_stride_h;
+  kp.lse = p->lse;
+  kp.n_q_heads = p->n_q_heads;
+  kp.group = p->n_q_heads / p->n_kv_heads;
+  kp.scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / sqrtf((float)kHeadDim);
+  kp.scale_log2 = kp.scale * 1.4426950408889634f;
+
+  dim3 grid(max_items, p->n_q_heads, 1);
+  if (p_in_tmem)
+    attn_fwd_kernel<true><<<grid, kAttnThreads, SmemLayout<true>::kDynamic, stream>>>(tq, tk, tv, tkc, tvc, kp);
+  else
+    attn_fwd_kernel<false><<<grid, kAttnThreads, SmemLayout<false>::kDynamic, stream>>>(tq, tk, tv, tkc, tvc, kp);
+  MAGI_CUDA_OK(ctx, cudaGetLastError());
+  return MAGI_OK;
+}
+
+}  // namespace magi

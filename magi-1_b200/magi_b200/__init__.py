@@ -1,0 +1,10 @@
+"""magi_b200: B200 (sm_100a) chunk-wise block-causal GQA attention core behind a C ABI.
+
+Importing the package loads libmagi_attn.so from the source tree and fails loudly if it is absent.
+"""
+from . import _lib
+from ._lib import MagiError, LIB_PATH
+from .ops import (ChunkPagedKVCache, Context, chunk_attn, flex_attn, head_block_copy, qk_norm_rope, varlen_attn)
+
+__all__ = ["ChunkPagedKVCache", "Context", "MagiError", "LIB_PATH", "chunk_attn", "flex_attn", "head_block_copy",
+           "qk_norm_rope", "varlen_attn"]

@@ -1,0 +1,261 @@
+"""PyTorch-facing shim over the C ABI: torch supplies device memory and streams, nothing else.
+
+Names and argument meaning mirror the reference's surface for this path:
+  flex_attn(...)            <-> the `flex_attention` callable of inference/model/dit/dit_module.py:1032-1043
+  qk_norm_rope(...)         <-> FullyParallelAttention.get_q / get_k (:953-980) after the projection
+  ChunkPagedKVCache         <-> Attention._allocate_key_and_value_memory / _full_adjust_key_and_value (:800-931)
+"""
+import ctypes as C
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import AttnParams, KVCacheDesc, PrologueParams, check, lib
+
+HEAD_DIM = 128
+
+
+class Context:
+    """One per (device); owns the plan workspace.  Calls sharing a context must be stream-ordered."""
+
+    _by_device = {}
+
+    def __init__(self, device: int):
+        h = C.c_void_p()
+        check(lib.magi_ctx_create(int(device), C.byref(h)))
+        self.handle = h
+        self.device = int(device)
+
+    @classmethod
+    def get(cls, device=None) -> "Context":
+        if device is None:
+            device = torch.cuda.current_device()
+        device = torch.device(device).index if not isinstance(device, int) else device
+        if device is None:
+            device = torch.cuda.current_device()
+        if device not in cls._by_device:
+            cls._by_device[device] = Context(device)
+        return cls._by_device[device]
+
+    def status(self, stream=None) -> int:
+        st = C.c_int(0)
+        check(lib.magi_ctx_status(self.handle, _stream(stream), C.byref(st)), self.handle)
+        return st.value
+
+    def close(self):
+        if self.handle:
+            lib.magi_ctx_destroy(self.handle)
+            self.handle = None
+
+
+def _stream(stream=None):
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+def _thd(t: torch.Tensor, name: str, dtype=torch.bfloat16):
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if t.dim() != 3 or t.shape[2] != HEAD_DIM or t.stride(2) != 1:
+        raise ValueError(f"{name} must be [tokens, heads, {HEAD_DIM}] with a contiguous last dim, got {tuple(t.shape)}")
+    return t
+
+
+def _ranges_dev(r, device) -> torch.Tensor:
+    if isinstance(r, torch.Tensor):
+        t = r.to(device=device, dtype=torch.int32)
+    else:
+        t = torch.as_tensor(np.asarray(r, dtype=np.int32), device=device)
+    return t.reshape(-1, 2).contiguous()
+
+
+def qk_norm_rope(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor], cos: Optional[torch.Tensor],
+                 sin: Optional[torch.Tensor], eps: float = 1e-6, norm_mode: str = "layernorm_1p",
+                 out: Optional[torch.Tensor] = None, heads_per_block: int = 0, stream=None) -> torch.Tensor:
+    """x bf16 [T,H,128] (any token/head strides) -> bf16 normed + rotated.
+
+    out=None gives the packed [T,H,128].  With heads_per_block = H/cp and out = [cp, T, H/cp, 128] the result
+    is the Ulysses send layout "(cp seq) hn hd" written directly.
+    """
+    _thd(x, "x")
+    T, H, _ = x.shape
+    ctx = Context.get(x.device)
+    if out is None:
+        out = torch.empty(T, H, HEAD_DIM, dtype=torch.bfloat16, device=x.device)
+    p = PrologueParams()
+    p.struct_size = C.sizeof(PrologueParams)
+    p.norm_mode = {"layernorm_1p": _lib.NORM_LAYERNORM_1P, "rmsnorm": _lib.NORM_RMSNORM_1P}[norm_mode]
+    p.x, p.x_stride_t, p.x_stride_h, p.T, p.H = x.data_ptr(), x.stride(0), x.stride(1), T, H
+    gamma = gamma.to(device=x.device, dtype=torch.float32).contiguous()
+    p.gamma = gamma.data_ptr()
+    if beta is not None:
+        beta = beta.to(device=x.device, dtype=torch.float32).contiguous()
+        p.beta = beta.data_ptr()
+    p.eps = eps
+    if cos is not None:
+        cos = cos.to(device=x.device, dtype=torch.float32).contiguous()
+        sin = sin.to(device=x.device, dtype=torch.float32).contiguous()
+        assert cos.shape == sin.shape and cos.shape[0] == T
+        p.rot_pairs, p.cos, p.sin = cos.shape[1], cos.data_ptr(), sin.data_ptr()
+    _fill_out(p, out, T, H, heads_per_block)
+    check(lib.magi_qk_norm_rope_fwd(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
+    return out
+
+
+def head_block_copy(x: torch.Tensor, out: torch.Tensor, heads_per_block: int = 0, stream=None) -> torch.Tensor:
+    """Strided bf16 copy [T,H,128] -> out with the same destination addressing as qk_norm_rope."""
+    _thd(x, "x")
+    T, H, _ = x.shape
+    ctx = Context.get(x.device)
+    p = PrologueParams()
+    p.struct_size = C.sizeof(PrologueParams)
+    p.x, p.x_stride_t, p.x_stride_h, p.T, p.H = x.data_ptr(), x.stride(0), x.stride(1), T, H
+    _fill_out(p, out, T, H, heads_per_block)
+    check(lib.magi_head_block_copy(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
+    return out
+
+
+def _fill_out(p, out, T, H, heads_per_block):
+    if out.dtype != torch.bfloat16 or not out.is_cuda or out.stride(-1) != 1:
+        raise ValueError("out must be a CUDA bf16 tensor with a contiguous last dim")
+    if heads_per_block and heads_per_block < H:
+        if out.dim() != 4 or out.shape[0] * heads_per_block != H or out.shape[1] < T or out.shape[2] != heads_per_block:
+            raise ValueError("blocked out must be [H/heads_per_block, >=T, heads_per_block, 128]")
+        p.out, p.out_stride_block, p.out_stride_t, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
+        p.heads_per_block = heads_per_block
+    else:
+        if out.dim() != 3 or out.shape[0] < T or out.shape[1] != H:
+            raise ValueError("out must be [>=T, H, 128]")
+        p.out, p.out_stride_t, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+
+
+class ChunkPagedKVCache:
+    """Pages of one chunk x one layer, K and V separate, bf16 or fp8 (+ per-(head,128-token) scales)."""
+
+    def __init__(self, n_layers: int, max_chunks: int, chunk_tokens: int, n_kv_heads: int, dtype: str = "bf16",
+                 device=None):
+        self.ctx = Context.get(device)
+        d = KVCacheDesc()
+        d.struct_size = C.sizeof(KVCacheDesc)
+        d.dtype = {"bf16": _lib.DTYPE_BF16, "fp8": _lib.DTYPE_FP8_E4M3}[dtype]
+        d.n_layers, d.max_chunks, d.chunk_tokens, d.n_kv_heads = n_layers, max_chunks, chunk_tokens, n_kv_heads
+        h = C.c_void_p()
+        check(lib.magi_kv_cache_create(self.ctx.handle, C.byref(d), C.byref(h)), self.ctx.handle)
+        self.handle = h
+        self.dtype = dtype
+        self.n_layers, self.max_chunks, self.chunk_tokens, self.n_kv_heads = n_layers, max_chunks, chunk_tokens, n_kv_heads
+
+    @property
+    def nbytes(self) -> int:
+        return lib.magi_kv_cache_bytes(self.handle)
+
+    def append(self, layer: int, chunk_id: int, k: torch.Tensor, v: torch.Tensor, token_offset: int = 0, stream=None):
+        _thd(k, "k"), _thd(v, "v")
+        assert k.shape == v.shape and k.shape[1] == self.n_kv_heads
+        check(lib.magi_kv_cache_append(self.handle, layer, chunk_id, k.data_ptr(), k.stride(0), k.stride(1),
+                                       v.data_ptr(), v.stride(0), v.stride(1), k.shape[0], token_offset,
+                                       _stream(stream)), self.ctx.handle)
+
+    def append_kv(self, layer: int, chunk_id: int, kv: torch.Tensor, token_offset: int = 0, stream=None):
+        """kv: the reference's fused layout [tokens, Hkv, 2*128] (K | V on the last dim)."""
+        self.append(layer, chunk_id, kv[..., :HEAD_DIM], kv[..., HEAD_DIM:], token_offset, stream)
+
+    def evict(self, chunk_id: int):
+        check(lib.magi_kv_cache_evict(self.handle, chunk_id), self.ctx.handle)
+
+    def read(self, layer: int, chunk_id: int, n_tokens: Optional[int] = None, token_offset: int = 0, stream=None):
+        n = self.chunk_tokens - token_offset if n_tokens is None else n_tokens
+        dev = torch.device("cuda", self.ctx.device)
+        k = torch.empty(n, self.n_kv_heads, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        v = torch.empty_like(k)
+        check(lib.magi_kv_cache_read(self.handle, layer, chunk_id, k.data_ptr(), v.data_ptr(), n, token_offset,
+                                     _stream(stream)), self.ctx.handle)
+        return k, v
+
+    def close(self):
+        if self.handle:
+            lib.magi_kv_cache_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def chunk_attn(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_ranges, k_ranges,
+               max_seqlen_q: int, max_seqlen_k: int = 0, softmax_scale: Optional[float] = None,
+               k_range_offsets=None, cache: Optional[ChunkPagedKVCache] = None, layer: int = 0,
+               prefix_chunk_ids: Sequence[int] = (), out: Optional[torch.Tensor] = None, return_lse: bool = True,
+               impl: str = "tcgen05", stream=None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """General entry: several k intervals per q-range (k_range_offsets) and a paged prefix."""
+    _thd(q, "q")
+    dev = q.device
+    ctx = Context.get(dev)
+    Tq, Hq, _ = q.shape
+    p = AttnParams()
+    p.struct_size = C.sizeof(AttnParams)
+    p.dtype = _lib.DTYPE_BF16
+    p.q, p.q_stride_t, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+    if k is not None and k.shape[0] > 0:
+        _thd(k, "k"), _thd(v, "v")
+        assert k.shape == v.shape
+        p.k, p.k_stride_t, p.k_stride_h = k.data_ptr(), k.stride(0), k.stride(1)
+        p.v, p.v_stride_t, p.v_stride_h = v.data_ptr(), v.stride(0), v.stride(1)
+        p.total_k, p.n_kv_heads = k.shape[0], k.shape[1]
+    else:
+        if cache is None:
+            raise ValueError("no keys: k is empty and there is no cache")
+        p.total_k, p.n_kv_heads = 0, cache.n_kv_heads
+    if out is None:
+        out = torch.empty(Tq, Hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+    p.out, p.o_stride_t, p.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+    lse = torch.empty(Tq, Hq, dtype=torch.float32, device=dev) if return_lse else None
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.total_q, p.n_q_heads = Tq, Hq
+    qr = _ranges_dev(q_ranges, dev)
+    kr = _ranges_dev(k_ranges, dev)
+    p.q_ranges, p.k_ranges = qr.data_ptr(), kr.data_ptr()
+    p.n_ranges, p.n_k_ranges = qr.shape[0], kr.shape[0]
+    ko = None
+    if k_range_offsets is not None:
+        ko = torch.as_tensor(np.asarray(k_range_offsets, dtype=np.int32), device=dev) \
+            if not isinstance(k_range_offsets, torch.Tensor) else k_range_offsets.to(device=dev, dtype=torch.int32).contiguous()
+        p.k_range_offsets = ko.data_ptr()
+    p.max_seqlen_q, p.max_seqlen_k = int(max_seqlen_q), int(max_seqlen_k)
+    p.softmax_scale = float(softmax_scale) if softmax_scale else 0.0
+    ids = None
+    if cache is not None and len(prefix_chunk_ids) > 0:
+        ids = (C.c_int32 * len(prefix_chunk_ids))(*[int(c) for c in prefix_chunk_ids])
+        p.cache, p.layer, p.n_prefix_chunks, p.prefix_chunk_ids = cache.handle, layer, len(prefix_chunk_ids), ids
+    fn = {"tcgen05": lib.magi_chunk_attn_fwd, "simt": lib.magi_chunk_attn_fwd_simt}[impl]
+    check(fn(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
+    # qr/kr/ko are consumed by a kernel already enqueued on this stream; torch's caching allocator only
+    # reuses their memory for later work on the same stream, so dropping them here is safe.
+    return out, lse
+
+
+def flex_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_ranges: torch.Tensor, k_ranges: torch.Tensor,
+              max_seqlen_q: int, max_seqlen_k: int, softmax_scale: Optional[float] = None,
+              deterministic: bool = False, disable_fwd_atomic_reduction: bool = True, **_unused):
+    """Drop-in for the reference's `flex_attention` (MagiAttention's flex_flash_attn_func surface as called at
+    inference/model/dit/dit_module.py:1032-1043): packed q [(b sq),Hq,128], k/v [(b skv),Hkv,128], int32 [n,2]
+    device ranges; returns (out, lse).  The kernel is deterministic and never reduces across CTAs, so
+    `deterministic` and `disable_fwd_atomic_reduction` are accepted and have nothing to switch.
+    Assign it with `dit_module.flex_attention = magi_b200.flex_attn`."""
+    return chunk_attn(q, k, v, q_ranges, k_ranges, max_seqlen_q, max_seqlen_k, softmax_scale)
+
+
+def varlen_attn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale=None):
+    """cu_seqlens convenience wrapper (sequence i of q attends to sequence i of k)."""
+    cq = torch.as_tensor(cu_seqlens_q, dtype=torch.int32)
+    ck = torch.as_tensor(cu_seqlens_k, dtype=torch.int32)
+    qr = torch.stack([cq[:-1], cq[1:]], dim=1)
+    kr = torch.stack([ck[:-1], ck[1:]], dim=1)
+    return chunk_attn(q, k, v, qr, kr, max_seqlen_q, max_seqlen_k, softmax_scale)
