@@ -1,0 +1,298 @@
+"""Benchmark of the chunk-causal attention hot path (prologue -> [Ulysses in] -> attention -> [Ulysses out]).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3|cfg1] [--impl ours|reference]
+
+One process per GPU (under torchrun for N > 1; RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the environment).
+Rank 0 prints ONE JSON line.  A "step" is one pass of the hot path over one batch of seeded synthetic inputs of
+the named configuration: per-head LayerNorm + 3D RoPE of Q and K, (for N > 1: head<->sequence all-to-all in),
+block-causal attention, (all-to-all out).  `value` = useful (unmasked) attention FLOPs of the whole job / step time.
+"""
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "magi-1_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np
+import torch
+
+WORKLOADS = {
+    # 24B-style 720p layer: 48/8 heads, 45x80 patches x 6 frames per chunk, 4 chunks, block-causal (cfg 3)
+    "cfg3": dict(name="24B-720p: Hq48/Hkv8 d128, 4 chunks x 21600 tok (T24 H45 W80), block-causal, bf16",
+                 hq=48, hkv=8, H=45, W=80, frames_per_chunk=6, n_chunks=4, seed=3),
+    # 4.5B-style layer: 24/8 heads, 30x52 patches x 6 frames per chunk, 4 chunks (cfg 1)
+    "cfg1": dict(name="4.5B-style: Hq24/Hkv8 d128, 4 chunks x 9360 tok (T24 H30 W52), block-causal, bf16",
+                 hq=24, hkv=8, H=30, W=52, frames_per_chunk=6, n_chunks=4, seed=1),
+}
+
+
+def useful_flops(hq, chunk_tokens, n_chunks):
+    pairs = sum((i + 1) for i in range(n_chunks)) * chunk_tokens * chunk_tokens
+    return 4.0 * 128 * hq * pairs
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return dict(bf16_burst=p["bf16_tflops"], bf16_sustained=p["bf16_tflops_sustained"], hbm=p["hbm_gbs"], src="measured")
+    except Exception:
+        return dict(bf16_burst=1590.0, bf16_sustained=1400.0, hbm=6650.0, src="fallback")
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap", nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                     nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                     nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown"}
+            while not self.stop_flag:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, nm in names.items():
+                    if r & bit:
+                        self.reasons.add(nm)
+                time.sleep(0.05)
+        except Exception as e:  # NVML unavailable: report that instead of inventing numbers
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+# ------------------------------------------------------------------------------------------------ reference arm
+def cpu_attention_sample(w, q_rows_per_range, threads):
+    """The reference's attention math in eager fp32 PyTorch on the host (oracle port), on a bounded sample:
+    one KV-head group, `q_rows_per_range` query rows of each of the chunk ranges against their full key ranges."""
+    from oracle import chunk_attn_oracle as O
+    torch.set_num_threads(threads)
+    C = w["H"] * w["W"] * w["frames_per_chunk"]
+    n, G = w["n_chunks"], w["hq"] // w["hkv"]
+    g = torch.Generator().manual_seed(w["seed"])
+    k = torch.randn(n * C, 1, 128, generator=g)
+    v = torch.randn(n * C, 1, 128, generator=g)
+    q = torch.randn(n * q_rows_per_range, G, 128, generator=g)
+    qr = [[i * q_rows_per_range, (i + 1) * q_rows_per_range] for i in range(n)]
+    segs = [[[0, (i + 1) * C]] for i in range(n)]
+    flops = 4.0 * 128 * G * q_rows_per_range * sum((i + 1) * C for i in range(n))
+    t0 = time.perf_counter()
+    O.range_attention(q, k, v, qr, segs)
+    dt = time.perf_counter() - t0
+    return flops, dt
+
+
+def run_reference(args, w, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows = 256
+    for _ in range(args.warmup):
+        cpu_attention_sample(w, 32, threads)
+    tot_f, tot_t = 0.0, 0.0
+    for _ in range(args.steps):
+        f, t = cpu_attention_sample(w, rows, threads)
+        tot_f += f
+        tot_t += t
+    val = tot_f / tot_t / 1e12
+    C = w["H"] * w["W"] * w["frames_per_chunk"]
+    sample = f"1 of {w['hkv']} KV-head groups, {rows} q rows of each of the {w['n_chunks']} chunk ranges vs their full key ranges, fp32 eager torch"
+    line = {"impl": "reference", "metric": "chunk_causal_attn_useful_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": tot_t / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w["name"], "chunk_tokens": C},
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ our arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, w, rank, world)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import magi_b200 as mb
+    from oracle import chunk_attn_oracle as O  # cpu_baseline leg and RoPE table only
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    cp = world
+    if cp > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    Hq, Hkv = w["hq"], w["hkv"]
+    C = w["H"] * w["W"] * w["frames_per_chunk"]
+    n = w["n_chunks"]
+    S = n * C
+    flops = useful_flops(Hq, C, n)
+    peaks = load_peaks()
+
+    # ---- synthetic inputs (seeded); every rank generates its own sequence slice of the pre-norm projections
+    splits = O.cp_split_sizes(S, cp)
+    off = sum(splits[:rank])
+    s_loc = splits[rank]
+    g = torch.Generator(device=dev).manual_seed(w["seed"] * 1000 + rank)
+    xq = torch.randn(s_loc, Hq, 128, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    xk = torch.randn(s_loc, Hkv, 128, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    xv = torch.randn(s_loc, Hkv, 128, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    gq, bq, gk, bk = [t.to(dev) for t in O.make_norm_params(w["seed"])]
+    sin, cos = O.rope_table(n * w["frames_per_chunk"], w["H"], w["W"])
+    sin, cos = sin[off:off + s_loc].contiguous().to(dev), cos[off:off + s_loc].contiguous().to(dev)
+    qr = torch.as_tensor(O.consecutive_q_ranges(n, C), device=dev)
+    kr = torch.as_tensor(O.default_k_ranges(n, C), device=dev)
+
+    if cp > 1:
+        from magi_b200.ulysses import UlyssesAttention
+        ua = UlyssesAttention(cp_group=dist.group.WORLD, n_q_heads=Hq, n_kv_heads=Hkv, split_sizes=splits)
+    q_buf = torch.empty(s_loc, Hq, 128, dtype=torch.bfloat16, device=dev)
+    k_buf = torch.empty(s_loc, Hkv, 128, dtype=torch.bfloat16, device=dev)
+    out_buf = torch.empty(s_loc, Hq, 128, dtype=torch.bfloat16, device=dev)
+    attn_ev = []
+
+    def step(record=False):
+        if cp == 1:
+            mb.qk_norm_rope(xq, gq, bq, cos, sin, out=q_buf)
+            mb.qk_norm_rope(xk, gk, bk, cos, sin, out=k_buf)
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            mb.chunk_attn(q_buf, k_buf, xv, qr, kr, C, S, out=out_buf, return_lse=False)
+            if record:
+                e1.record()
+                attn_ev.append((e0, e1))
+            return out_buf
+        return ua.forward(xq, xk, xv, gq, bq, gk, bk, cos, sin, qr, kr, C, S, attn_events=attn_ev if record else None)
+
+    def barrier():
+        if cp > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    assert mb.Context.get(local_rank).status() == 0, "device status word reports a failure during warm-up"
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        step(record=True)
+    t1.record()
+    barrier()
+    sampler.stop_flag = True
+    ms = t0.elapsed_time(t1)
+    attn_ms = sum(a.elapsed_time(b) for a, b in attn_ev) / max(1, len(attn_ev))
+    if cp > 1:
+        tt = torch.tensor([ms, attn_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, attn_ms = tt.tolist()
+    ms_per_step = ms / args.steps
+    sampler.join(timeout=1.0)
+
+    # ---- end to end through the public API with host buffers (H2D of the step's inputs, D2H of its output)
+    e2e = None
+    if not args.no_e2e:
+        hq_, hk_, hv_ = xq.cpu().pin_memory(), xk.cpu().pin_memory(), xv.cpu().pin_memory()
+        ho = torch.empty(s_loc, Hq, 128, dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step():
+            xq.copy_(hq_, non_blocking=True)
+            xk.copy_(hk_, non_blocking=True)
+            xv.copy_(hv_, non_blocking=True)
+            o = step()
+            ho.copy_(o, non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k_e2e = max(3, args.steps // 2)
+        a.record()
+        for _ in range(k_e2e):
+            e2e_step()
+        b.record()
+        barrier()
+        e_ms = a.elapsed_time(b)
+        if cp > 1:
+            tt = torch.tensor([e_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            e_ms = tt.item()
+        h2d = (hq_.numel() + hk_.numel() + hv_.numel()) * 2
+        e2e = {"value": flops / (e_ms / k_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e_ms / k_e2e,
+               "h2d_bytes_per_step": h2d * cp, "d2h_bytes_per_step": ho.numel() * 2 * cp}
+
+    if rank == 0:
+        cpu_b = None
+        if cp == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            cpu_attention_sample(w, 16, threads)
+            f, t = cpu_attention_sample(w, 256, threads)
+            cpu_b = {"value": f / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port", "seconds": t,
+                     "sample": f"1 of {Hkv} KV-head groups, 256 q rows of each of the {n} chunk ranges vs their full key ranges, fp32 eager torch"}
+        per_gpu_flops = flops / cp
+        achieved = per_gpu_flops / (attn_ms * 1e-3) / 1e12
+        line = {
+            "metric": "chunk_causal_attn_useful_tflops", "value": flops / (ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": cp, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["name"], "chunk_tokens": C, "useful_tflop_per_step": flops / 1e12,
+                       "parallelism": f"ulysses-cp{cp}" if cp > 1 else "single-gpu",
+                       "l2": "inputs (>= 0.6 GB per step) exceed the 126 MB L2; no explicit flush",
+                       "step": "qk layernorm+rope prologue, attention" + (", all-to-all in/out" if cp > 1 else "")},
+            "attn_ms": attn_ms,
+            "pct_of_bf16_burst_peak": 100 * achieved / peaks["bf16_burst"],
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["bf16_sustained"], "peak_kind": f"{peaks['src']} sustained cuBLAS bf16",
+                         "frac_of_burst": achieved / peaks["bf16_burst"], "traffic": None,
+                         "kernel": "attn_fwd_kernel", "per_gpu_tflop_per_launch": per_gpu_flops / 1e12},
+            "clocks": sampler.summary(),
+            "gpu_launches": args.steps * (4 if cp == 1 else 6),
+        }
+        if cpu_b:
+            line["cpu_baseline"] = cpu_b
+        if e2e:
+            line["e2e"] = e2e
+        print(json.dumps(line), flush=True)
+    if cp > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
