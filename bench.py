@@ -33,6 +33,9 @@ WORKLOADS = {
 }
 
 
+CPU_SAMPLE_ROWS = 4096  # q rows per chunk range in the CPU baseline sample (about 10 s of host work at cfg3)
+
+
 def useful_flops(hq, chunk_tokens, n_chunks):
     pairs = sum((i + 1) for i in range(n_chunks)) * chunk_tokens * chunk_tokens
     return 4.0 * 128 * hq * pairs
@@ -103,7 +106,7 @@ def run_reference(args, w, rank, world):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    rows = 256
+    rows = CPU_SAMPLE_ROWS // 4
     for _ in range(args.warmup):
         cpu_attention_sample(w, 32, threads)
     tot_f, tot_t = 0.0, 0.0
@@ -147,7 +150,7 @@ def main():
         args.warmup = 3
 
     import magi_b200 as mb
-    from oracle import chunk_attn_oracle as O  # cpu_baseline leg and RoPE table only
+    from magi_b200 import host
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     cp = world
@@ -162,18 +165,18 @@ def main():
     peaks = load_peaks()
 
     # ---- synthetic inputs (seeded); every rank generates its own sequence slice of the pre-norm projections
-    splits = O.cp_split_sizes(S, cp)
+    splits = host.cp_split_sizes(S, cp)
     off = sum(splits[:rank])
     s_loc = splits[rank]
     g = torch.Generator(device=dev).manual_seed(w["seed"] * 1000 + rank)
     xq = torch.randn(s_loc, Hq, 128, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
     xk = torch.randn(s_loc, Hkv, 128, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
     xv = torch.randn(s_loc, Hkv, 128, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
-    gq, bq, gk, bk = [t.to(dev) for t in O.make_norm_params(w["seed"])]
-    sin, cos = O.rope_table(n * w["frames_per_chunk"], w["H"], w["W"])
+    gq, bq, gk, bk = [t.to(dev) for t in host.synthetic_norm_params(w["seed"])]
+    sin, cos = host.split_sin_cos(host.rotary_table(n * w["frames_per_chunk"], w["H"], w["W"]))
     sin, cos = sin[off:off + s_loc].contiguous().to(dev), cos[off:off + s_loc].contiguous().to(dev)
-    qr = torch.as_tensor(O.consecutive_q_ranges(n, C), device=dev)
-    kr = torch.as_tensor(O.default_k_ranges(n, C), device=dev)
+    qr = torch.as_tensor(host.q_ranges_for_chunks(n, C), device=dev)
+    kr = torch.as_tensor(host.default_k_ranges(n, C), device=dev)
 
     if cp > 1:
         from magi_b200.ulysses import UlyssesAttention
@@ -262,9 +265,9 @@ def main():
         if cp == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             cpu_attention_sample(w, 16, threads)
-            f, t = cpu_attention_sample(w, 256, threads)
+            f, t = cpu_attention_sample(w, CPU_SAMPLE_ROWS, threads)
             cpu_b = {"value": f / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port", "seconds": t,
-                     "sample": f"1 of {Hkv} KV-head groups, 256 q rows of each of the {n} chunk ranges vs their full key ranges, fp32 eager torch"}
+                     "sample": f"1 of {Hkv} KV-head groups, {CPU_SAMPLE_ROWS} q rows of each of the {n} chunk ranges vs their full key ranges, fp32 eager torch"}
         per_gpu_flops = flops / cp
         achieved = per_gpu_flops / (attn_ms * 1e-3) / 1e12
         line = {
