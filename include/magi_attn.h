@@ -182,6 +182,25 @@ MAGI_API int magi_chunk_attn_fwd(magi_ctx* ctx, const magi_attn_params* p, void*
  * numerical failure can be attributed to the plan or to the tensor-core kernel; it is not a dispatch target. */
 MAGI_API int magi_chunk_attn_fwd_simt(magi_ctx* ctx, const magi_attn_params* p, void* stream);
 
+/* Attention forward for callers that are not allowed to allocate device memory.  It has no counterpart in the
+ * reference.  Who needs it: a serving process that has already handed (nearly) all of HBM to its own arenas - KV pools
+ * sized to fill the GPU, a framework allocator that owns the rest - where a late cudaMalloc, even of the 640 KiB a
+ * context needs, can fail or stall the device; and plug-in hosts that forbid raw CUDA allocations in their workers.
+ * Same arithmetic and same kernel as magi_chunk_attn_fwd (bf16), but no context: the planner's scratch is a fixed
+ * 640 KiB array inside the library image (one per GPU that loads the library, kept until exit).  The caller passes
+ * inputs and outputs as usual; nothing here calls cudaMalloc/cudaFree or any allocating routine.
+ *   - Limits: n_ranges <= 1024, n_ranges * ceil(max_seqlen_q / 256) <= 16384, n_k_ranges + n_prefix_chunks <= 4096;
+ *     anything larger is rejected with MAGI_E_NOMEM and a message, nothing is launched.
+ *   - Works on the CURRENT device.  The first call on each device also does a one-time set-up (symbol address
+ *     lookup, shared-memory opt-in); make that first call outside any stream capture, from one thread.
+ *   - Every call on a device shares the one scratch array, which keeps the previous call's contents; the entry point
+ *     clears the part that must start at zero.  Two calls whose GPU work can overlap (different streams, or several
+ *     threads) race on it: keep the calls of one device stream-ordered.
+ *   - status_dev (device int32*, may be NULL) receives, stream-ordered, the planner/kernel status word
+ *     (0, MAGI_E_RANGE or MAGI_E_TIMEOUT).  err/err_len (host buffer, may be NULL/0) receives the failure text. */
+MAGI_API int magi_chunk_attn_fwd_noalloc(const magi_attn_params* p, void* stream, int32_t* status_dev, char* err,
+                                         int err_len);
+
 /* bf16 [T,H,128] -> e4m3 [T,H,128] + fp32 scales [n_blocks,H] (scale = absmax/448 per (128-token block, head),
  * blocks counted from each multiple of chunk_tokens).  No reference counterpart: the reference's attention is
  * never FP8 (its fp8 path is the linear layers, inference/model/dit/dit_module.py:431-487). */

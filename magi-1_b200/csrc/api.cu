@@ -348,3 +348,97 @@ extern "C" int magi_chunk_attn_fwd(magi_ctx* ctx, const magi_attn_params* p, voi
 extern "C" int magi_chunk_attn_fwd_simt(magi_ctx* ctx, const magi_attn_params* p, void* stream) {
   return attn_common(ctx, p, stream, 2);
 }
+
+// ------------------------------------------------------------------------------------------- no-allocation entry
+// Plan scratch for callers that must not allocate: lives in the library image, one copy per GPU that loads the
+// library, held until the process exits.  Same layout and capacity as a context's workspace (kPlanBytes = 640 KiB:
+// at most 16384 work items, 8192 K/V segments, 1024 ranges).
+static __device__ __align__(256) unsigned char g_noalloc_plan_scratch[magi::kPlanBytes];
+
+namespace {
+constexpr int kNoAllocMaxDevices = 64;
+magi_ctx g_noalloc_ctx[kNoAllocMaxDevices];   // host-side bookkeeping only (device index, SM count, scratch address)
+bool g_noalloc_ready[kNoAllocMaxDevices];
+
+void copy_err(char* dst, int dst_len, const char* src) {
+  if (!dst || dst_len <= 0) return;
+  strncpy(dst, src, (size_t)dst_len - 1);
+  dst[dst_len - 1] = 0;
+}
+}  // namespace
+
+extern "C" int magi_chunk_attn_fwd_noalloc(const magi_attn_params* p, void* stream, int32_t* status_dev, char* err,
+                                           int err_len) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) {
+    copy_err(err, err_len, "no-alloc attention: no usable current CUDA device");
+    return MAGI_E_CUDA;
+  }
+  magi_ctx* ctx = &g_noalloc_ctx[dev];
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (!g_noalloc_ready[dev]) {
+    // One-time set-up for this device, done with it current.  g_noalloc_plan_scratch named from host code is only a
+    // stand-in for the symbol, not a device address: the address a kernel may use has to be asked for.
+    int major = 0, sms = 0;
+    void* scratch = nullptr;
+    cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e == cudaSuccess && major != 10) {
+      copy_err(err, err_len, "no-alloc attention: device is not sm_100");
+      return MAGI_E_ARCH;
+    }
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&scratch, g_noalloc_plan_scratch);
+    if (e != cudaSuccess || !scratch) {
+      copy_err(err, err_len, cudaGetErrorString(e));
+      return MAGI_E_CUDA;
+    }
+    memset(ctx, 0, sizeof(*ctx));
+    ctx->device = dev;
+    ctx->sm_count = sms;
+    ctx->workspace = scratch;
+    int rc = attn_init_device(ctx);  // raises the kernels' dynamic shared memory limit; allocates nothing
+    if (rc) {
+      copy_err(err, err_len, ctx->err);
+      return rc;
+    }
+    g_noalloc_ready[dev] = true;
+  }
+  if (!p || p->struct_size != sizeof(magi_attn_params)) {
+    copy_err(err, err_len, "no-alloc attention: bad struct_size");
+    return MAGI_E_BADARG;
+  }
+  if (p->dtype != MAGI_DTYPE_BF16) {
+    copy_err(err, err_len, "no-alloc attention: bf16 only");
+    return MAGI_E_BADARG;
+  }
+  const int rows_per_item = kTileM * kTilesPerCta;
+  const long long items = (long long)p->n_ranges * ((p->max_seqlen_q + rows_per_item - 1) / rows_per_item);
+  if (p->n_ranges > kMaxRanges || items > kMaxItems || (long long)p->n_k_ranges + p->n_prefix_chunks > kMaxSegs / 2) {
+    if (err && err_len > 0)
+      snprintf(err, (size_t)err_len,
+               "no-alloc attention: problem exceeds the fixed scratch (%d ranges <= %d, %lld work items <= %d, "
+               "%d k intervals + %d prefix chunks <= %d)",
+               p->n_ranges, kMaxRanges, items, kMaxItems, p->n_k_ranges, p->n_prefix_chunks, kMaxSegs / 2);
+    return MAGI_E_NOMEM;
+  }
+  // The scratch keeps what the previous call left: the header (item count, status word) must start from zero.
+  cudaError_t e = cudaMemsetAsync(ctx->workspace, 0, sizeof(PlanHeader), st);
+  if (e != cudaSuccess) {
+    copy_err(err, err_len, cudaGetErrorString(e));
+    return MAGI_E_CUDA;
+  }
+  int rc = attn_common(ctx, p, stream, 0);
+  if (rc) {
+    copy_err(err, err_len, ctx->err);
+    return rc;
+  }
+  if (status_dev) {
+    e = cudaMemcpyAsync(status_dev, reinterpret_cast<char*>(ctx->workspace) + offsetof(PlanHeader, status), sizeof(int32_t),
+                        cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) {
+      copy_err(err, err_len, cudaGetErrorString(e));
+      return MAGI_E_CUDA;
+    }
+  }
+  return MAGI_OK;
+}

@@ -17,7 +17,7 @@ EXPORTS = [
     "magi_version", "magi_strerror", "magi_ctx_create", "magi_ctx_destroy", "magi_last_error", "magi_ctx_status",
     "magi_qk_norm_rope_fwd", "magi_head_block_copy", "magi_kv_cache_create", "magi_kv_cache_destroy",
     "magi_kv_cache_append", "magi_kv_cache_evict", "magi_kv_cache_read", "magi_kv_cache_bytes",
-    "magi_chunk_attn_fwd", "magi_chunk_attn_fwd_simt", "magi_quantize_e4m3_block128",
+    "magi_chunk_attn_fwd", "magi_chunk_attn_fwd_simt", "magi_quantize_e4m3_block128", "magi_chunk_attn_fwd_noalloc",
 ]
 
 
@@ -83,6 +83,7 @@ def _load():
         "magi_chunk_attn_fwd": (C.c_int, [vp, C.POINTER(AttnParams), vp]),
         "magi_chunk_attn_fwd_simt": (C.c_int, [vp, C.POINTER(AttnParams), vp]),
         "magi_quantize_e4m3_block128": (C.c_int, [vp, vp, i64, i64, i32, i32, i32, vp, vp, vp]),
+        "magi_chunk_attn_fwd_noalloc": (C.c_int, [C.POINTER(AttnParams), vp, vp, C.c_char_p, i32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -259,3 +259,37 @@ def varlen_attn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
     qr = torch.stack([cq[:-1], cq[1:]], dim=1)
     kr = torch.stack([ck[:-1], ck[1:]], dim=1)
     return chunk_attn(q, k, v, qr, kr, max_seqlen_q, max_seqlen_k, softmax_scale)
+
+
+def chunk_attn_noalloc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_ranges: torch.Tensor, k_ranges: torch.Tensor,
+                       max_seqlen_q: int, out: torch.Tensor, lse: Optional[torch.Tensor] = None,
+                       status: Optional[torch.Tensor] = None, softmax_scale: Optional[float] = None, stream=None) -> None:
+    """Attention for hosts that may not allocate on the device (all of HBM already belongs to somebody's arena).
+
+    Every tensor is supplied by the caller - q/k/v bf16 [tokens, heads, 128], int32 device ranges [n,2], the bf16
+    `out`, optionally an fp32 `lse` [tokens, Hq] and a 1-element int32 `status` - and neither this function nor the
+    library entry point behind it (magi_chunk_attn_fwd_noalloc) allocates device memory: the planner's scratch is a
+    fixed array inside the library.  Calls on one device must be stream-ordered (they share that array); the first
+    call per device does a little set-up and should not sit inside a stream capture."""
+    _thd(q, "q"), _thd(k, "k"), _thd(v, "v"), _thd(out, "out")
+    for name, r in (("q_ranges", q_ranges), ("k_ranges", k_ranges)):
+        if not (isinstance(r, torch.Tensor) and r.is_cuda and r.dtype == torch.int32 and r.is_contiguous() and r.dim() == 2):
+            raise ValueError(f"{name} must be a contiguous int32 CUDA tensor [n, 2] supplied by the caller")
+    p = AttnParams()
+    p.struct_size = C.sizeof(AttnParams)
+    p.dtype = _lib.DTYPE_BF16
+    p.q, p.q_stride_t, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+    p.k, p.k_stride_t, p.k_stride_h = k.data_ptr(), k.stride(0), k.stride(1)
+    p.v, p.v_stride_t, p.v_stride_h = v.data_ptr(), v.stride(0), v.stride(1)
+    p.out, p.o_stride_t, p.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.total_q, p.total_k, p.n_q_heads, p.n_kv_heads = q.shape[0], k.shape[0], q.shape[1], k.shape[1]
+    p.q_ranges, p.k_ranges = q_ranges.data_ptr(), k_ranges.data_ptr()
+    p.n_ranges, p.n_k_ranges = q_ranges.shape[0], k_ranges.shape[0]
+    p.max_seqlen_q = int(max_seqlen_q)
+    p.softmax_scale = float(softmax_scale) if softmax_scale else 0.0
+    err = C.create_string_buffer(512)
+    rc = lib.magi_chunk_attn_fwd_noalloc(C.byref(p), _stream(stream), status.data_ptr() if status is not None else None,
+                                         err, len(err))
+    if rc != _lib.MAGI_OK:
+        raise _lib.MagiError(rc, err.value.decode())
