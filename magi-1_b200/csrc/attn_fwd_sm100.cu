@@ -248,24 +248,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int c = 0; c < kTileN; ++c)
             if (c >= valid) s[c] = 0xff800000u;  // -inf
         }
-        float mx = __uint_as_float(s[0]);
+        // row maximum with 8 independent chains (a single 127-long dependent chain costs ~500 cycles)
+        float mxa[8];
 #pragma unroll
-        for (int c = 1; c < kTileN; ++c) mx = fmaxf(mx, __uint_as_float(s[c]));
+        for (int c = 0; c < 8; ++c) mxa[c] = __uint_as_float(s[c]);
+#pragma unroll
+        for (int c = 8; c < kTileN; ++c) mxa[c & 7] = fmaxf(mxa[c & 7], __uint_as_float(s[c]));
+        const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
+                               fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
         // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8 larger.
         const float m_new = fmaxf(m_used, mx);
         const bool need = (m_new - m_used) * sl2 > 8.0f;
         const float m_cur = need ? m_new : m_used;
         const float alpha = need ? ex2((m_used - m_new) * sl2) : 1.0f;
         const float neg_m = -m_cur * sl2;
-        float rowsum0 = 0.f, rowsum1 = 0.f;
+        float rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < kTileN; c += 2) {
+        for (int c = 0; c < kTileN; c += 4) {
           const float p0 = ex2(fmaf(__uint_as_float(s[c]), sl2, neg_m));
           const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), sl2, neg_m));
-          rowsum0 += p0;
-          rowsum1 += p1;
+          const float p2 = ex2(fmaf(__uint_as_float(s[c + 2]), sl2, neg_m));
+          const float p3 = ex2(fmaf(__uint_as_float(s[c + 3]), sl2, neg_m));
+          rs[0] += p0;
+          rs[1] += p1;
+          rs[2] += p2;
+          rs[3] += p3;
           s[c >> 1] = pack_bf16x2(p0, p1);
+          s[(c >> 1) + 1] = pack_bf16x2(p2, p3);
         }
+        const float rowsum0 = rs[0] + rs[2], rowsum1 = rs[1] + rs[3];
         if constexpr (kPInTmem) {
           tmem_st32(tS, s);
           tmem_st32(tS + 32, s + 32);
