@@ -86,7 +86,11 @@ typedef struct {
                                 + t*out_stride_t + (h % heads_per_block)*out_stride_h + d         */
   int64_t out_stride_t, out_stride_h, out_stride_block;
   int32_t heads_per_block;   /* 0 or >= H: no blocking */
-  int32_t reserved;
+  int32_t x_heads_per_block; /* source blocking (the inverse re-layout "(cp sq) hn hd -> sq (cp hn) hd" after the
+                                output all-to-all, context_parallel.py:596): element (t,h,d) is read at
+                                x + (h / x_heads_per_block)*x_stride_block + t*x_stride_t + (h % x_heads_per_block)*x_stride_h + d.
+                                0 or >= H: no blocking */
+  int64_t x_stride_block;
 } magi_prologue_params;
 MAGI_API int magi_qk_norm_rope_fwd(magi_ctx* ctx, const magi_prologue_params* p, void* stream);
 

@@ -13,7 +13,8 @@ namespace magi {
 
 struct PrologueKernelParams {
   const __nv_bfloat16* x;
-  int64_t x_stride_t, x_stride_h;
+  int64_t x_stride_t, x_stride_h, x_stride_block;
+  int x_heads_per_block;
   int T, H;
   const float* gamma;
   const float* beta;
@@ -68,7 +69,10 @@ __global__ void __launch_bounds__(256) prologue_kernel(PrologueKernelParams p) {
       if (r < n_rows) {
         tt[i] = (int)(r / p.H);
         hh[i] = (int)(r - (int64_t)tt[i] * p.H);
-        raw[i] = __ldg(reinterpret_cast<const uint2*>(p.x + (int64_t)tt[i] * p.x_stride_t + (int64_t)hh[i] * p.x_stride_h + d));
+        const int xb = p.x_heads_per_block > 0 ? hh[i] / p.x_heads_per_block : 0;
+        const int xh = p.x_heads_per_block > 0 ? hh[i] - xb * p.x_heads_per_block : hh[i];
+        raw[i] = __ldg(reinterpret_cast<const uint2*>(p.x + (int64_t)xb * p.x_stride_block + (int64_t)tt[i] * p.x_stride_t +
+                                                      (int64_t)xh * p.x_stride_h + d));
       }
     }
 #pragma unroll
@@ -122,7 +126,8 @@ static int check_prologue(magi_ctx* ctx, const magi_prologue_params* p, bool nor
   if (!p || p->struct_size != sizeof(magi_prologue_params)) return set_err(ctx, MAGI_E_BADARG, "prologue: bad struct_size");
   if (!p->x || !p->out || p->T < 0 || p->H <= 0) return set_err(ctx, MAGI_E_BADARG, "prologue: null tensor or bad shape");
   if ((reinterpret_cast<uintptr_t>(p->x) & 7) || (reinterpret_cast<uintptr_t>(p->out) & 7) || (p->x_stride_t & 3) ||
-      (p->x_stride_h & 3) || (p->out_stride_t & 3) || (p->out_stride_h & 3) || (p->out_stride_block & 3))
+      (p->x_stride_h & 3) || (p->x_stride_block & 3) || (p->out_stride_t & 3) || (p->out_stride_h & 3) ||
+      (p->out_stride_block & 3))
     return set_err(ctx, MAGI_E_ALIGN, "prologue: pointers must be 8-byte aligned and strides multiples of 4 elements");
   if (norm_rope) {
     if (!p->gamma) return set_err(ctx, MAGI_E_BADARG, "prologue: gamma is required");
@@ -147,6 +152,8 @@ static int launch_prologue(magi_ctx* ctx, const magi_prologue_params* p, bool no
   k.x = reinterpret_cast<const __nv_bfloat16*>(p->x);
   k.x_stride_t = p->x_stride_t;
   k.x_stride_h = p->x_stride_h;
+  k.x_stride_block = p->x_stride_block;
+  k.x_heads_per_block = (p->x_heads_per_block > 0 && p->x_heads_per_block < p->H) ? p->x_heads_per_block : 0;
   k.T = p->T;
   k.H = p->H;
   k.gamma = p->gamma;

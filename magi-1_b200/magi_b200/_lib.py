@@ -29,7 +29,7 @@ class PrologueParams(C.Structure):
         ("gamma", C.c_void_p), ("beta", C.c_void_p), ("eps", C.c_float), ("rot_pairs", C.c_int32),
         ("cos", C.c_void_p), ("sin", C.c_void_p),
         ("out", C.c_void_p), ("out_stride_t", C.c_int64), ("out_stride_h", C.c_int64), ("out_stride_block", C.c_int64),
-        ("heads_per_block", C.c_int32), ("reserved", C.c_int32),
+        ("heads_per_block", C.c_int32), ("x_heads_per_block", C.c_int32), ("x_stride_block", C.c_int64),
     ]
 
 

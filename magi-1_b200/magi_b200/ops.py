@@ -108,13 +108,26 @@ def qk_norm_rope(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tens
 
 
 def head_block_copy(x: torch.Tensor, out: torch.Tensor, heads_per_block: int = 0, stream=None) -> torch.Tensor:
-    """Strided bf16 copy [T,H,128] -> out with the same destination addressing as qk_norm_rope."""
-    _thd(x, "x")
-    T, H, _ = x.shape
+    """Strided bf16 copy -> out with the same destination addressing as qk_norm_rope.
+
+    x is [T,H,128], or a source-blocked [B, T, H/B, 128] ("(cp sq) hn hd", what the output all-to-all delivers),
+    which is read as the logical [T, H, 128] with head h = b*(H/B) + h'."""
+    if x.dim() == 4:
+        if x.dtype != torch.bfloat16 or not x.is_cuda or x.shape[3] != HEAD_DIM or x.stride(3) != 1:
+            raise ValueError("blocked x must be a CUDA bf16 [B, T, H/B, 128] tensor with a contiguous last dim")
+        B, T, hb, _ = x.shape
+        H = B * hb
+    else:
+        _thd(x, "x")
+        T, H, _ = x.shape
     ctx = Context.get(x.device)
     p = PrologueParams()
     p.struct_size = C.sizeof(PrologueParams)
-    p.x, p.x_stride_t, p.x_stride_h, p.T, p.H = x.data_ptr(), x.stride(0), x.stride(1), T, H
+    if x.dim() == 4:
+        p.x, p.x_stride_block, p.x_stride_t, p.x_stride_h = x.data_ptr(), x.stride(0), x.stride(1), x.stride(2)
+        p.x_heads_per_block, p.T, p.H = hb, T, H
+    else:
+        p.x, p.x_stride_t, p.x_stride_h, p.T, p.H = x.data_ptr(), x.stride(0), x.stride(1), T, H
     _fill_out(p, out, T, H, heads_per_block)
     check(lib.magi_head_block_copy(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
     return out

@@ -1,0 +1,156 @@
+"""Ulysses context parallelism for the attention core: heads are split across the CP ranks, every rank sees the
+full sequence for its heads.  Mirrors inference/infra/parallelism/context_parallel.py:381-423 (all_to_all_input_split /
+all_to_all_output_split) and UlyssesScheduler.get_attn_and_xattn_with_fused_kv_comm (:503-548, :550-597):
+
+    K|V prologue -> a2a(K|V) || Q prologue -> a2a(Q) -> [KV cache] -> attention per head group || a2a(O of previous group)
+
+Differences from the reference, all on the data-movement side:
+  * the prologue kernels write the send layout "(cp seq) hn hd" directly (no rearrange().contiguous() pass), K and V
+    into one fused [.., 256] buffer so one exchange carries both (as the reference's fused-KV path);
+  * the attention kernel reads K and V as strided halves of the received buffer (no chunk().contiguous());
+  * the received O blocks "(cp sq) hn hd" are put into "sq (cp hn) hd" by one strided copy kernel.
+torch.distributed (NCCL over NVLink, gloo in CPU tests) is the plumbing for the exchange itself.
+"""
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+HEAD_DIM = 128
+
+
+class UlyssesExchange:
+    """The two all-to-alls, on whatever device the tensors live on (NCCL for CUDA, gloo for CPU tensors)."""
+
+    def __init__(self, group, split_sizes: Sequence[int]):
+        self.group = group
+        self.cp = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.split_sizes = [int(s) for s in split_sizes]
+        if len(self.split_sizes) != self.cp:
+            raise ValueError(f"split_sizes has {len(self.split_sizes)} entries for a group of {self.cp}")
+        self.s_local = self.split_sizes[self.rank]
+        self.s_total = sum(self.split_sizes)
+
+    def scatter_heads(self, send: torch.Tensor, recv: Optional[torch.Tensor] = None, async_op: bool = True):
+        """send [cp, s_local, hn, d] (block r goes to rank r)  ->  recv [s_total, hn, d] (all tokens, own heads).
+        Returns (recv, work)."""
+        if send.shape[0] != self.cp or send.shape[1] != self.s_local or not send.is_contiguous():
+            raise ValueError(f"send must be contiguous [cp={self.cp}, s_local={self.s_local}, hn, d], got {tuple(send.shape)}")
+        if recv is None:
+            recv = torch.empty((self.s_total,) + tuple(send.shape[2:]), dtype=send.dtype, device=send.device)
+        work = dist.all_to_all_single(recv, send.view((self.cp * self.s_local,) + tuple(send.shape[2:])),
+                                      output_split_sizes=self.split_sizes, group=self.group, async_op=async_op)
+        return recv, work
+
+    def gather_heads(self, full: torch.Tensor, recv: Optional[torch.Tensor] = None, async_op: bool = True):
+        """full [s_total, hn, d] (all tokens, own heads)  ->  recv [cp, s_local, hn, d] (own tokens, block r = heads of rank r)."""
+        if full.shape[0] != self.s_total or not full.is_contiguous():
+            raise ValueError(f"full must be contiguous [s_total={self.s_total}, hn, d], got {tuple(full.shape)}")
+        if recv is None:
+            recv = torch.empty((self.cp, self.s_local) + tuple(full.shape[1:]), dtype=full.dtype, device=full.device)
+        work = dist.all_to_all_single(recv.view((self.cp * self.s_local,) + tuple(full.shape[1:])), full,
+                                      input_split_sizes=self.split_sizes, group=self.group, async_op=async_op)
+        return recv, work
+
+
+def kv_head_replication(n_kv_heads: int, cp: int) -> int:
+    """KV heads are repeated when there are more ranks than heads (context_parallel.py:393-394)."""
+    if cp % n_kv_heads == 0 and cp != n_kv_heads and cp > n_kv_heads:
+        return cp // n_kv_heads
+    if n_kv_heads % cp != 0:
+        raise ValueError(f"{n_kv_heads} KV heads cannot be split over {cp} ranks")
+    return 1
+
+
+class UlyssesAttention:
+    """Prologue + exchange + attention + exchange for one layer on one CP rank (CUDA)."""
+
+    def __init__(self, cp_group, n_q_heads: int, n_kv_heads: int, split_sizes: Sequence[int], overlap_degree: int = 1):
+        from . import ops
+        self.ops = ops
+        self.ex = UlyssesExchange(cp_group, split_sizes)
+        cp = self.ex.cp
+        if n_q_heads % cp:
+            raise ValueError(f"{n_q_heads} q heads cannot be split over {cp} ranks")
+        self.rep = kv_head_replication(n_kv_heads, cp)
+        self.hq, self.hkv = n_q_heads, n_kv_heads * self.rep
+        self.hq_loc, self.hkv_loc = self.hq // cp, self.hkv // cp
+        if self.hq_loc % self.hkv_loc:
+            raise ValueError("local q heads must be a multiple of local kv heads")
+        g = self.hq_loc // self.hkv_loc
+        if overlap_degree == -1:
+            overlap_degree = g
+        if overlap_degree < 1 or g % overlap_degree:
+            raise ValueError(f"overlap_degree {overlap_degree} must divide the GQA group size {g}")
+        self.overlap = overlap_degree
+        self._bufs = {}
+
+    def _buf(self, name, shape, device):
+        t = self._bufs.get(name)
+        if t is None or tuple(t.shape) != tuple(shape) or t.device != device:
+            t = torch.empty(shape, dtype=torch.bfloat16, device=device)
+            self._bufs[name] = t
+        return t
+
+    def forward(self, xq, xk, xv, gq, bq, gk, bk, cos, sin, q_ranges, k_ranges, max_seqlen_q, max_seqlen_k,
+                eps: float = 1e-6, norm_mode: str = "layernorm_1p", cache=None, layer: int = 0,
+                prefix_chunk_ids: Sequence[int] = (), k_range_offsets=None, attn_events: Optional[list] = None):
+        """xq [s_local, Hq, 128], xk / xv [s_local, Hkv, 128]: this rank's tokens, all heads (projection outputs).
+        cos / sin: this rank's rows of the rotary table.  Ranges are in full-sequence token coordinates.
+        Returns O [s_local, Hq, 128] for this rank's tokens, heads in global order."""
+        ops, ex = self.ops, self.ex
+        cp, s_loc, S = ex.cp, ex.s_local, ex.s_total
+        dev = xq.device
+        if self.rep > 1:
+            xk = xk.repeat_interleave(self.rep, dim=1)
+            xv = xv.repeat_interleave(self.rep, dim=1)
+        kv_send = self._buf("kv_send", (cp, s_loc, self.hkv_loc, 2 * HEAD_DIM), dev)
+        ops.qk_norm_rope(xk, gk, bk, cos, sin, eps, norm_mode, out=kv_send[..., :HEAD_DIM], heads_per_block=self.hkv_loc)
+        ops.head_block_copy(xv, kv_send[..., HEAD_DIM:], heads_per_block=self.hkv_loc)
+        kv_recv, w_kv = ex.scatter_heads(kv_send, self._buf("kv_recv", (S, self.hkv_loc, 2 * HEAD_DIM), dev))
+        q_send = self._buf("q_send", (cp, s_loc, self.hq_loc, HEAD_DIM), dev)
+        ops.qk_norm_rope(xq, gq, bq, cos, sin, eps, norm_mode, out=q_send, heads_per_block=self.hq_loc)
+        q_recv, w_q = ex.scatter_heads(q_send, self._buf("q_recv", (S, self.hq_loc, HEAD_DIM), dev))
+        w_kv.wait()
+        k_full, v_full = kv_recv[..., :HEAD_DIM], kv_recv[..., HEAD_DIM:]
+        w_q.wait()
+
+        out = self._buf("out", (s_loc, self.hq, HEAD_DIM), dev)
+        o_full = self._buf("o_full", (self.overlap, S, self.hq_loc // self.overlap, HEAD_DIM), dev)
+        o_recv = self._buf("o_recv", (self.overlap, cp, s_loc, self.hq_loc // self.overlap, HEAD_DIM), dev)
+        g = self.hq_loc // self.hkv_loc
+        gsub = g // self.overlap
+        q_grp = q_recv.view(S, self.hkv_loc, g, HEAD_DIM)
+        pending = None
+        for i in range(self.overlap):
+            # head group i: sub-heads [i*gsub, (i+1)*gsub) of every local KV head (GQA-aware split, context_parallel.py:570-578)
+            qi = q_grp[:, :, i * gsub:(i + 1) * gsub].reshape(S, self.hkv_loc * gsub, HEAD_DIM) if self.overlap > 1 else q_recv
+            if attn_events is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            ops.chunk_attn(qi, k_full, v_full, q_ranges, k_ranges, max_seqlen_q, max_seqlen_k, out=o_full[i], return_lse=False,
+                           k_range_offsets=k_range_offsets, cache=cache, layer=layer, prefix_chunk_ids=prefix_chunk_ids)
+            if attn_events is not None:
+                e1.record()
+                attn_events.append((e0, e1))
+            if pending is not None:
+                self._finish(pending, out, gsub)
+            _, w = ex.gather_heads(o_full[i], o_recv[i])
+            pending = (i, w, o_recv[i])
+        self._finish(pending, out, gsub)
+        return out
+
+    def _finish(self, pending, out, gsub):
+        """Wait for the exchange of head group i and place its blocks: "(cp sq) hn hd -> sq (cp hn) hd"."""
+        i, w, o_recv = pending
+        w.wait()
+        if self.overlap == 1:
+            self.ops.head_block_copy(o_recv, out)
+        else:
+            # group i holds sub-heads [i*gsub, (i+1)*gsub) of each local kv head: scatter them to their global positions
+            cp, s_loc = o_recv.shape[0], o_recv.shape[1]
+            g = self.hq_loc // self.hkv_loc
+            dst = out.view(s_loc, cp, self.hkv_loc, g, HEAD_DIM)[:, :, :, i * gsub:(i + 1) * gsub]
+            src = o_recv.view(cp, s_loc, self.hkv_loc, gsub, HEAD_DIM).permute(1, 0, 2, 3, 4)
+            dst.copy_(src)

@@ -46,7 +46,8 @@ def test_struct_layouts_match_the_header(tmp_path):
     fields = {
         "magi_attn_params": ["q", "k", "v", "out", "lse", "total_q", "q_ranges", "n_ranges", "softmax_scale", "cache",
                              "prefix_chunk_ids", "q_scale", "scale_chunk_tokens"],
-        "magi_prologue_params": ["x", "T", "gamma", "eps", "cos", "out", "out_stride_block", "heads_per_block"],
+        "magi_prologue_params": ["x", "T", "gamma", "eps", "cos", "out", "out_stride_block", "heads_per_block",
+                                 "x_heads_per_block", "x_stride_block"],
         "magi_kv_cache_desc": ["dtype", "chunk_tokens", "n_kv_heads"],
     }
     body = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]

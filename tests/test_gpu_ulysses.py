@@ -1,0 +1,69 @@
+"""Ulysses context-parallel attention on 2 (or 4) GPUs of one box against the single-sequence CPU oracle.
+Skipped when fewer than 2 GPUs are visible.  NVLS is switched off for the child ranks."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, overlap):
+    for p in (ROOT, os.path.join(ROOT, "magi-1_b200"), os.path.join(ROOT, "tests")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import magi_b200 as mb
+    from magi_b200 import host
+    from magi_b200.ulysses import UlyssesAttention
+    from oracle import chunk_attn_oracle as O
+    from gpu_util import as_segments, assert_close, oracle_on_rows
+
+    C, n, Hq, Hkv = 331, 3, 8, 4          # 993 tokens: uneven split over 2 and 4 ranks
+    S = C * n
+    g = torch.Generator().manual_seed(77)
+    xq = torch.randn(S, Hq, 128, generator=g).to(torch.bfloat16)
+    xk = torch.randn(S, Hkv, 128, generator=g).to(torch.bfloat16)
+    xv = torch.randn(S, Hkv, 128, generator=g).to(torch.bfloat16)
+    gq, bq, gk, bk = host.synthetic_norm_params(7)
+    sin, cos = host.split_sin_cos(host.rotary_table(3, 1, 331))
+    splits = host.cp_split_sizes(S, world)
+    off = sum(splits[:rank])
+    sl = slice(off, off + splits[rank])
+    qr, kr = host.q_ranges_for_chunks(n, C), host.default_k_ranges(n, C)
+    ua = UlyssesAttention(dist.group.WORLD, Hq, Hkv, splits, overlap_degree=overlap)
+    dev = torch.device("cuda", rank)
+    for _ in range(2):  # second pass reuses the buffers
+        out = ua.forward(xq[sl].to(dev), xk[sl].to(dev), xv[sl].to(dev), gq, bq, gk, bk, cos[sl], sin[sl],
+                         torch.as_tensor(qr, device=dev), torch.as_tensor(kr, device=dev), C, S)
+    torch.cuda.synchronize()
+    assert mb.Context.get(rank).status() == 0
+    # oracle on the full sequence, restricted to this rank's rows
+    q_ref = O.qk_prologue(xq, gq, bq, cos, sin).float()
+    k_ref = O.qk_prologue(xk, gk, bk, cos, sin).float()
+    rows, ref, _ = oracle_on_rows(q_ref, k_ref, xv.float(), qr, as_segments(kr), torch.arange(off, off + splits[rank]))
+    assert torch.equal(rows, torch.arange(off, off + splits[rank]))
+    assert_close(out, ref, what=f"ulysses cp{world} rank {rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,overlap", [(2, 1), (2, 2), (4, 1)])
+def test_ulysses_attention_matches_oracle(world, overlap):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(world, _free_port(), overlap), nprocs=world, join=True)
