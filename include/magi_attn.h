@@ -180,6 +180,10 @@ typedef struct {
   const float* v_scale;
   int32_t scale_chunk_tokens;
   int32_t reserved;
+  /* FP8 only, optional: second e4m3 term of Q (rounding residual of the first, same scales, same strides as q).
+   * When given, the kernel runs its two-term mode: S = (Q8 + Q8_lo) K8^T and O += (P8 + P8_lo) V8, which removes the
+   * quantisation noise of Q and of P (K and V stay single e4m3) at the price of twice the UMMA work. */
+  const void* q_lo;
 } magi_attn_params;
 MAGI_API int magi_chunk_attn_fwd(magi_ctx* ctx, const magi_attn_params* p, void* stream);
 /* Diagnostic twin: same plan, same arguments (bf16 only), plain CUDA-core arithmetic in fp32.  It exists so a
@@ -206,10 +210,11 @@ MAGI_API int magi_chunk_attn_fwd_noalloc(const magi_attn_params* p, void* stream
                                          int err_len);
 
 /* bf16 [T,H,128] -> e4m3 [T,H,128] + fp32 scales [n_blocks,H] (scale = absmax/448 per (128-token block, head),
- * blocks counted from each multiple of chunk_tokens).  No reference counterpart: the reference's attention is
- * never FP8 (its fp8 path is the linear layers, inference/model/dit/dit_module.py:431-487). */
+ * blocks counted from each multiple of chunk_tokens).  x8_lo (optional, same shape) receives the e4m3 rounding
+ * residual e4m3(x/scale - x8).  No reference counterpart: the reference's attention is never FP8 (its fp8 path is
+ * the linear layers, inference/model/dit/dit_module.py:431-487). */
 MAGI_API int magi_quantize_e4m3_block128(magi_ctx* ctx, const void* x, int64_t stride_t, int64_t stride_h, int T, int H,
-                                int chunk_tokens, void* x8, float* scales, void* stream);
+                                int chunk_tokens, void* x8, void* x8_lo, float* scales, void* stream);
 
 #ifdef __cplusplus
 }

@@ -389,7 +389,9 @@ int make_tile_map(magi_ctx* ctx, CUtensorMap* m, const void* base, int64_t strid
 }
 
 // Opt in to > 48 KB of dynamic shared memory; called once per context with its device current.
+int attn_fp8_init_device(magi_ctx* ctx);
 int attn_init_device(magi_ctx* ctx) {
+  if (int rc = attn_fp8_init_device(ctx)) return rc;
   MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SmemLayout<true>::kDynamic));
   MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,

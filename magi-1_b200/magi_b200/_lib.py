@@ -55,7 +55,7 @@ class AttnParams(C.Structure):
         ("cache", C.c_void_p), ("layer", C.c_int32), ("n_prefix_chunks", C.c_int32),
         ("prefix_chunk_ids", C.POINTER(C.c_int32)),
         ("q_scale", C.c_void_p), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
-        ("scale_chunk_tokens", C.c_int32), ("reserved", C.c_int32),
+        ("scale_chunk_tokens", C.c_int32), ("reserved", C.c_int32), ("q_lo", C.c_void_p),
     ]
 
 
@@ -82,7 +82,7 @@ def _load():
         "magi_kv_cache_bytes": (C.c_int64, [vp]),
         "magi_chunk_attn_fwd": (C.c_int, [vp, C.POINTER(AttnParams), vp]),
         "magi_chunk_attn_fwd_simt": (C.c_int, [vp, C.POINTER(AttnParams), vp]),
-        "magi_quantize_e4m3_block128": (C.c_int, [vp, vp, i64, i64, i32, i32, i32, vp, vp, vp]),
+        "magi_quantize_e4m3_block128": (C.c_int, [vp, vp, i64, i64, i32, i32, i32, vp, vp, vp, vp]),
         "magi_chunk_attn_fwd_noalloc": (C.c_int, [C.POINTER(AttnParams), vp, vp, C.c_char_p, i32]),
     }
     for name, (res, args) in sig.items():

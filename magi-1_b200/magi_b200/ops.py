@@ -206,18 +206,35 @@ def chunk_attn(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
                max_seqlen_q: int, max_seqlen_k: int = 0, softmax_scale: Optional[float] = None,
                k_range_offsets=None, cache: Optional[ChunkPagedKVCache] = None, layer: int = 0,
                prefix_chunk_ids: Sequence[int] = (), out: Optional[torch.Tensor] = None, return_lse: bool = True,
-               impl: str = "tcgen05", stream=None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-    """General entry: several k intervals per q-range (k_range_offsets) and a paged prefix."""
-    _thd(q, "q")
+               impl: str = "tcgen05", stream=None, q_scale: Optional[torch.Tensor] = None,
+               k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None,
+               scale_chunk_tokens: int = 0, q_lo: Optional[torch.Tensor] = None
+               ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """General entry: several k intervals per q-range (k_range_offsets) and a paged prefix.
+
+    bf16 q/k/v, or e4m3 q/k/v (torch.float8_e4m3fn) with the fp32 block scales of quantize_e4m3 (out stays bf16)."""
+    fp8 = q.dtype == torch.float8_e4m3fn
+    in_dtype = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    _thd(q, "q", in_dtype)
     dev = q.device
     ctx = Context.get(dev)
     Tq, Hq, _ = q.shape
     p = AttnParams()
     p.struct_size = C.sizeof(AttnParams)
-    p.dtype = _lib.DTYPE_BF16
+    p.dtype = _lib.DTYPE_FP8_E4M3 if fp8 else _lib.DTYPE_BF16
+    if fp8:
+        if q_scale is None or scale_chunk_tokens <= 0:
+            raise ValueError("fp8 attention needs q_scale and scale_chunk_tokens")
+        p.q_scale, p.scale_chunk_tokens = q_scale.data_ptr(), int(scale_chunk_tokens)
+        if k_scale is not None:
+            p.k_scale, p.v_scale = k_scale.data_ptr(), v_scale.data_ptr()
+        if q_lo is not None:
+            if q_lo.shape != q.shape or q_lo.stride() != q.stride() or q_lo.dtype != q.dtype:
+                raise ValueError("q_lo must have q's shape, strides and dtype")
+            p.q_lo = q_lo.data_ptr()
     p.q, p.q_stride_t, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
     if k is not None and k.shape[0] > 0:
-        _thd(k, "k"), _thd(v, "v")
+        _thd(k, "k", in_dtype), _thd(v, "v", in_dtype)
         assert k.shape == v.shape
         p.k, p.k_stride_t, p.k_stride_h = k.data_ptr(), k.stride(0), k.stride(1)
         p.v, p.v_stride_t, p.v_stride_h = v.data_ptr(), v.stride(0), v.stride(1)
@@ -252,6 +269,24 @@ def chunk_attn(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
     # qr/kr/ko are consumed by a kernel already enqueued on this stream; torch's caching allocator only
     # reuses their memory for later work on the same stream, so dropping them here is safe.
     return out, lse
+
+
+def quantize_e4m3(x: torch.Tensor, chunk_tokens: int, stream=None, residual: bool = False):
+    """bf16 [T,H,128] (strided) -> (e4m3 [T,H,128], fp32 scales [ceil(T/chunk)*ceil(chunk/128), H]).
+    128-token blocks are counted from each multiple of chunk_tokens; scale = absmax / 448.
+    residual=True also returns the second e4m3 term e4m3(x/scale - x8) as a third value."""
+    _thd(x, "x")
+    T, H, _ = x.shape
+    ctx = Context.get(x.device)
+    nb = (chunk_tokens + 127) // 128
+    n_chunks = (T + chunk_tokens - 1) // chunk_tokens
+    x8 = torch.empty(T, H, HEAD_DIM, dtype=torch.float8_e4m3fn, device=x.device)
+    scales = torch.ones(max(1, n_chunks * nb), H, dtype=torch.float32, device=x.device)
+    lo = torch.empty_like(x8) if residual else None
+    check(lib.magi_quantize_e4m3_block128(ctx.handle, x.data_ptr(), x.stride(0), x.stride(1), T, H, int(chunk_tokens),
+                                          x8.data_ptr(), lo.data_ptr() if residual else None, scales.data_ptr(),
+                                          _stream(stream)), ctx.handle)
+    return (x8, scales, lo) if residual else (x8, scales)
 
 
 def flex_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_ranges: torch.Tensor, k_ranges: torch.Tensor,

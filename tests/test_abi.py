@@ -45,7 +45,7 @@ def test_struct_layouts_match_the_header(tmp_path):
     probe = tmp_path / "probe.c"
     fields = {
         "magi_attn_params": ["q", "k", "v", "out", "lse", "total_q", "q_ranges", "n_ranges", "softmax_scale", "cache",
-                             "prefix_chunk_ids", "q_scale", "scale_chunk_tokens"],
+                             "prefix_chunk_ids", "q_scale", "scale_chunk_tokens", "q_lo"],
         "magi_prologue_params": ["x", "T", "gamma", "eps", "cos", "out", "out_stride_block", "heads_per_block",
                                  "x_heads_per_block", "x_stride_block"],
         "magi_kv_cache_desc": ["dtype", "chunk_tokens", "n_kv_heads"],
