@@ -30,6 +30,12 @@ WORKLOADS = {
     # 4.5B-style layer: 24/8 heads, 30x52 patches x 6 frames per chunk, 4 chunks (cfg 1)
     "cfg1": dict(name="4.5B-style: Hq24/Hkv8 d128, 4 chunks x 9360 tok (T24 H30 W52), block-causal, bf16",
                  hq=24, hkv=8, H=30, W=52, frames_per_chunk=6, n_chunks=4, seed=1),
+    # KV-cache decode step (cfg 2): batch 2 (CFG), 4 denoising chunks each, chunk i sees its own cached prefix of i chunks + itself
+    "cfg2": dict(name="4.5B-style decode: b2 x 4 denoising chunks x 9360 tok, own paged bf16 prefix (0..3 chunks) + self",
+                 hq=24, hkv=8, H=30, W=52, frames_per_chunk=6, n_chunks=4, seed=2, decode=True, batch=2, n_prefix=3),
+    # FP8 e4m3 of cfg 3 (cfg 4): chunks 0..2 read from an fp8 page cache, chunk 3 fresh; two-term Q/P
+    "cfg4": dict(name="24B-720p FP8 e4m3: Hq48/Hkv8 d128, 4 q chunks x 21600 tok, K/V of chunks 0-2 from fp8 pages, chunk 3 fresh",
+                 hq=48, hkv=8, H=45, W=80, frames_per_chunk=6, n_chunks=4, seed=3, fp8=True),
 }
 
 
@@ -39,6 +45,28 @@ CPU_SAMPLE_ROWS = 4096  # q rows per chunk range in the CPU baseline sample (abo
 def useful_flops(hq, chunk_tokens, n_chunks):
     pairs = sum((i + 1) for i in range(n_chunks)) * chunk_tokens * chunk_tokens
     return 4.0 * 128 * hq * pairs
+
+
+def measure_fp8_peak(dev):
+    """Dense e4m3 GEMM 8192^3 through torch._scaled_mm (cuBLASLt), best of 10, CUDA events: the FP8 denominator that
+    the driver-written peaks file does not carry."""
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=dev)
+        best = 1e9
+        for i in range(13):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                best = min(best, e0.elapsed_time(e1))
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception as e:  # pragma: no cover
+        return None
 
 
 def load_peaks():
@@ -178,27 +206,89 @@ def main():
     qr = torch.as_tensor(host.q_ranges_for_chunks(n, C), device=dev)
     kr = torch.as_tensor(host.default_k_ranges(n, C), device=dev)
 
+    special = w.get("decode") or w.get("fp8")
+    if special and cp > 1:
+        raise SystemExit(f"workload {args.workload} is a single-GPU benchmark line")
     if cp > 1:
         from magi_b200.ulysses import UlyssesAttention
         ua = UlyssesAttention(cp_group=dist.group.WORLD, n_q_heads=Hq, n_kv_heads=Hkv, split_sizes=splits)
-    q_buf = torch.empty(s_loc, Hq, 128, dtype=torch.bfloat16, device=dev)
-    k_buf = torch.empty(s_loc, Hkv, 128, dtype=torch.bfloat16, device=dev)
-    out_buf = torch.empty(s_loc, Hq, 128, dtype=torch.bfloat16, device=dev)
     attn_ev = []
+    n_launch = [0]
 
-    def step(record=False):
-        if cp == 1:
-            mb.qk_norm_rope(xq, gq, bq, cos, sin, out=q_buf)
-            mb.qk_norm_rope(xk, gk, bk, cos, sin, out=k_buf)
-            if record:
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-            mb.chunk_attn(q_buf, k_buf, xv, qr, kr, C, S, out=out_buf, return_lse=False)
-            if record:
-                e1.record()
-                attn_ev.append((e0, e1))
+    def timed_attn(record, fn):
+        if record:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        r = fn()
+        if record:
+            e1.record()
+            attn_ev.append((e0, e1))
+        return r
+
+    if w.get("decode"):
+        # ---- cfg 2: b x n denoising chunks; the clean prefix chunks live in the paged cache (filled outside the timed region)
+        B, NP = w["batch"], w["n_prefix"]
+        flops = B * flops
+        g2 = torch.Generator(device=dev).manual_seed(w["seed"] * 1000 + 7)
+        xq = torch.randn(B * S, Hq, 128, generator=g2, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        xk = torch.randn(B * S, Hkv, 128, generator=g2, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        xv = torch.randn(B * S, Hkv, 128, generator=g2, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        cache = mb.ChunkPagedKVCache(n_layers=1, max_chunks=B * NP, chunk_tokens=C, n_kv_heads=Hkv, device=local_rank)
+        for pc in range(B * NP):
+            kvp = torch.randn(C, Hkv, 256, generator=g2, device=dev, dtype=torch.float32).to(torch.bfloat16)
+            cache.append_kv(0, pc, kvp)
+        sin_b, cos_b = sin.repeat(B, 1), cos.repeat(B, 1)
+        qr = torch.as_tensor(host.q_ranges_for_chunks(n, C, batch=B), device=dev)
+        kr_np, ko_np = host.own_prefix_k_segments(n, C, NP, batch=B)
+        kr, ko = torch.as_tensor(kr_np, device=dev), torch.as_tensor(ko_np, device=dev)
+        q_buf, k_buf, out_buf = torch.empty_like(xq), torch.empty_like(xk), torch.empty_like(xq)
+        s_loc = B * S
+
+        def step(record=False):
+            mb.qk_norm_rope(xq, gq, bq, cos_b, sin_b, out=q_buf)
+            mb.qk_norm_rope(xk, gk, bk, cos_b, sin_b, out=k_buf)
+            timed_attn(record, lambda: mb.chunk_attn(q_buf, k_buf, xv, qr, kr, C, (NP + 1) * C, k_range_offsets=ko, out=out_buf,
+                                                     return_lse=False, cache=cache, layer=0, prefix_chunk_ids=list(range(B * NP))))
+            n_launch[0] = 4
             return out_buf
-        return ua.forward(xq, xk, xv, gq, bq, gk, bk, cos, sin, qr, kr, C, S, attn_events=attn_ev if record else None)
+    elif w.get("fp8"):
+        # ---- cfg 4: fp8; K/V of chunks 0..n-2 sit in an fp8 page cache, the last chunk is fresh
+        cache = mb.ChunkPagedKVCache(n_layers=1, max_chunks=n - 1, chunk_tokens=C, n_kv_heads=Hkv, dtype="fp8", device=local_rank)
+        k_all = mb.qk_norm_rope(xk, gk, bk, cos, sin)
+        for pc in range(n - 1):
+            cache.append(0, pc, k_all[pc * C:(pc + 1) * C], xv[pc * C:(pc + 1) * C])
+        del k_all
+        xk_cur, xv_cur = xk[(n - 1) * C:], xv[(n - 1) * C:]
+        cos_cur, sin_cur = cos[(n - 1) * C:].contiguous(), sin[(n - 1) * C:].contiguous()
+        q_buf = torch.empty(S, Hq, 128, dtype=torch.bfloat16, device=dev)
+        k_buf = torch.empty(C, Hkv, 128, dtype=torch.bfloat16, device=dev)
+        out_buf = torch.empty(S, Hq, 128, dtype=torch.bfloat16, device=dev)
+
+        def step(record=False):
+            mb.qk_norm_rope(xq, gq, bq, cos, sin, out=q_buf)
+            mb.qk_norm_rope(xk_cur, gk, bk, cos_cur, sin_cur, out=k_buf)
+            q8, qs, q8lo = mb.quantize_e4m3(q_buf, C, residual=True)
+            k8, ks = mb.quantize_e4m3(k_buf, C)
+            v8, vs = mb.quantize_e4m3(xv_cur, C)
+            timed_attn(record, lambda: mb.chunk_attn(q8, k8, v8, qr, kr, C, S, out=out_buf, return_lse=False, cache=cache, layer=0,
+                                                     prefix_chunk_ids=list(range(n - 1)), q_scale=qs, k_scale=ks, v_scale=vs,
+                                                     scale_chunk_tokens=C, q_lo=q8lo))
+            n_launch[0] = 7
+            return out_buf
+    else:
+        q_buf = torch.empty(s_loc, Hq, 128, dtype=torch.bfloat16, device=dev)
+        k_buf = torch.empty(s_loc, Hkv, 128, dtype=torch.bfloat16, device=dev)
+        out_buf = torch.empty(s_loc, Hq, 128, dtype=torch.bfloat16, device=dev)
+
+        def step(record=False):
+            if cp == 1:
+                mb.qk_norm_rope(xq, gq, bq, cos, sin, out=q_buf)
+                mb.qk_norm_rope(xk, gk, bk, cos, sin, out=k_buf)
+                timed_attn(record, lambda: mb.chunk_attn(q_buf, k_buf, xv, qr, kr, C, S, out=out_buf, return_lse=False))
+                n_launch[0] = 4
+                return out_buf
+            n_launch[0] = 7
+            return ua.forward(xq, xk, xv, gq, bq, gk, bk, cos, sin, qr, kr, C, S, attn_events=attn_ev if record else None)
 
     def barrier():
         if cp > 1:
@@ -232,7 +322,7 @@ def main():
     e2e = None
     if not args.no_e2e:
         hq_, hk_, hv_ = xq.cpu().pin_memory(), xk.cpu().pin_memory(), xv.cpu().pin_memory()
-        ho = torch.empty(s_loc, Hq, 128, dtype=torch.bfloat16).pin_memory()
+        ho = torch.empty(out_buf.shape[0] if cp == 1 else s_loc, Hq, 128, dtype=torch.bfloat16).pin_memory()
 
         def e2e_step():
             xq.copy_(hq_, non_blocking=True)
@@ -273,7 +363,7 @@ def main():
         line = {
             "metric": "chunk_causal_attn_useful_tflops", "value": flops / (ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s",
             "n_gpus": cp, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3" if w.get("fp8") else "bf16", "data": "synthetic",
             "config": {"workload": w["name"], "chunk_tokens": C, "useful_tflop_per_step": flops / 1e12,
                        "parallelism": f"ulysses-cp{cp}" if cp > 1 else "single-gpu",
                        "l2": "inputs (>= 0.6 GB per step) exceed the 126 MB L2; no explicit flush",
@@ -285,8 +375,12 @@ def main():
                          "frac_of_burst": achieved / peaks["bf16_burst"], "traffic": None,
                          "kernel": "attn_fwd_kernel", "per_gpu_tflop_per_launch": per_gpu_flops / 1e12},
             "clocks": sampler.summary(),
-            "gpu_launches": args.steps * (4 if cp == 1 else 6),
+            "gpu_launches": args.steps * n_launch[0],
         }
+        if w.get("fp8"):
+            fp8_peak = measure_fp8_peak(dev)
+            line["roofline"]["fp8_peak_measured_tflops"] = fp8_peak
+            line["roofline"]["frac_of_fp8_peak"] = achieved / fp8_peak if fp8_peak else None
         if cpu_b:
             line["cpu_baseline"] = cpu_b
         if e2e:
