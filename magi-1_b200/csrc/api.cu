@@ -8,7 +8,7 @@
 
 namespace magi {
 
-int launch_attn_bf16(magi_ctx* ctx, const magi_attn_params* p, int max_items, bool p_in_tmem, cudaStream_t stream);
+int launch_attn_bf16(magi_ctx* ctx, const magi_attn_params* p, int max_items, cudaStream_t stream);
 int launch_attn_fp8(magi_ctx* ctx, const magi_attn_params* p, int max_items, cudaStream_t stream);
 int launch_attn_simt(magi_ctx* ctx, const magi_attn_params* p, int max_items, cudaStream_t stream);
 int attn_init_device(magi_ctx* ctx);
@@ -329,20 +329,13 @@ static int attn_common(magi_ctx* ctx, const magi_attn_params* p, void* stream, i
   int rc;
   if (impl == 2) rc = launch_attn_simt(ctx, p, (int)max_items, st);
   else if (fp8) rc = launch_attn_fp8(ctx, p, (int)max_items, st);
-  else rc = launch_attn_bf16(ctx, p, (int)max_items, impl == 0, st);
+  else rc = launch_attn_bf16(ctx, p, (int)max_items, st);
   if (prev != ctx->device) cudaSetDevice(prev);
   return rc;
 }
 
 extern "C" int magi_chunk_attn_fwd(magi_ctx* ctx, const magi_attn_params* p, void* stream) {
-  // MAGI_ATTN_P_SMEM=1 selects the build of the kernel that stages P through shared memory instead of TMEM
-  // (a bring-up switch for A/B checks on hardware; both are tcgen05 kernels).
-  static int p_smem = -1;
-  if (p_smem < 0) {
-    const char* e = getenv("MAGI_ATTN_P_SMEM");
-    p_smem = (e && e[0] == '1') ? 1 : 0;
-  }
-  return attn_common(ctx, p, stream, p_smem ? 1 : 0);
+  return attn_common(ctx, p, stream, 0);
 }
 
 extern "C" int magi_chunk_attn_fwd_simt(magi_ctx* ctx, const magi_attn_params* p, void* stream) {

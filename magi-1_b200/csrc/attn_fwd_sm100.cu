@@ -11,7 +11,7 @@
 //   warps 8-11  softmax for Q tile 1   } row sum need no shuffles.  They also rescale O and store the output.
 //
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512), fp32.  P (bf16) overwrites the first
-// 64 columns of its S and is the A operand of the PV UMMA straight from TMEM.
+// 64 columns of its S and is the A operand of the PV UMMA straight from TMEM (no shared-memory round trip).
 // While warpgroup 0 does softmax on S0 the tensor pipe runs the UMMAs of tile 1, and vice versa.
 #include <cuda_bf16.h>
 #include <math.h>
@@ -38,13 +38,36 @@ struct AttnKernelParams {
   float scale_log2;   // scale * log2(e)
 };
 
-template <bool kPInTmem>
+// Optional device-side timeline (compiled only with -DMAGI_TRACE, never in the shipped library): CTA (0,0) stamps
+// clock64() at the hand-off points of its first kTraceIters K/V tiles.
+#ifdef MAGI_TRACE
+#ifndef MAGI_TRACE_J0
+#define MAGI_TRACE_J0 0
+#endif
+#ifndef MAGI_TRACE_HEAD
+#define MAGI_TRACE_HEAD 0
+#endif
+constexpr int kTraceIters = 24;
+constexpr int kTraceEvents = 8;
+__device__ long long g_trace[4][kTraceIters][kTraceEvents];  // [0] UMMA issuer, [1] softmax WG0, [2] softmax WG1, [3] producer (per fill)
+__device__ long long g_cta_log[8192][4];  // per CTA: globaltimer start, end, n_tiles, smid
+#define MAGI_STAMP(role, j, ev)                                                         \
+  do {                                                                                  \
+    if (blockIdx.x == 0 && blockIdx.y == MAGI_TRACE_HEAD && (j) >= MAGI_TRACE_J0 && (j) < MAGI_TRACE_J0 + kTraceIters) \
+      g_trace[role][(j) - MAGI_TRACE_J0][ev] = clock64();                                                            \
+  } while (0)
+#else
+#define MAGI_STAMP(role, j, ev) do { } while (0)
+#endif
+
+// Shared memory: Q (2 tiles, 64 KB) + a ring of 5 K/V stages (160 KB): K_j and V_j alternate through the ring, so the
+// producer runs 2.5 K/V tile pairs ahead of the UMMAs.  (With 4 stages the TMA round trip was exposed: ~1000 of the
+// ~4100 cycles per K/V tile were the UMMA issuer waiting for data.)
 struct SmemLayout {
-  static constexpr int kStages = kPInTmem ? 4 : 3;
+  static constexpr int kStages = 5;
   static constexpr int kQ = 0;
   static constexpr int kRing = kQ + kTilesPerCta * kTileBytes;
-  static constexpr int kP = kRing + kStages * kTileBytes;
-  static constexpr int kBar = kP + (kPInTmem ? 0 : kTilesPerCta * kTileBytes);
+  static constexpr int kBar = kRing + kStages * kTileBytes;
   // barriers: q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2]
   static constexpr int kNumBars = 1 + 2 * kStages + 6;
   static constexpr int kMisc = kBar + kNumBars * 8;
@@ -62,12 +85,11 @@ __device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile_saddr, int k) {
   return umma_smem_desc(tile_saddr + k * 2048, kHalfBytes, 1024, kSw128);
 }
 
-template <bool kPInTmem>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
                 const __grid_constant__ CUtensorMap tm_vc, const AttnKernelParams p) {
-  using L = SmemLayout<kPInTmem>;
+  using L = SmemLayout;
   constexpr int kStages = L::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -82,6 +104,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+#ifdef MAGI_TRACE
+  long long cta_t0 = 0;
+  if (threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(cta_t0));
+#endif
   if (n_tiles == 0) {  // a q-range with no keys: define the output as zeros, lse = -inf
     for (int idx = threadIdx.x; idx < it.q_rows * (kHeadDim / 8); idx += blockDim.x) {
       const int r = idx / (kHeadDim / 8), c = idx % (kHeadDim / 8);
@@ -150,8 +176,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int kv = 0; kv < 2; ++kv, ++fill) {
             const int stage = fill % kStages;
             const int use = fill / kStages;
+            MAGI_STAMP(3, fill, 0);
             if (use > 0) ok = mbar_wait(&kv_empty[stage], (use & 1) ^ 1, abort_flag);
             if (!ok) break;
+            MAGI_STAMP(3, fill, 1);
             mbar_expect_tx(&kv_full[stage], kTileBytes);
             const CUtensorMap* m = kv ? mv : mk;
             tma_load_3d(ring + stage * kTileBytes, m, &kv_full[stage], 0, kv_head, sg.row0 + t0);
@@ -162,57 +190,79 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ UMMA issuer
+    // ------------------------------------------------------------------ UMMA issuer (one thread)
+    // Order per K/V tile j:  PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1): while the tensor pipe works for one Q tile the
+    // other tile's warpgroup does its softmax.  The loop is kept to a few instructions per UMMA (a single thread
+    // shares its scheduler with two softmax warps): descriptors are (lo, hi) halves advanced by 32-bit adds,
+    // accumulate flags are compile-time, ring stage / parity are running counters.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(kTileM, kTileN, 1, 1, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc(kTileM, kHeadDim, 1, 1, 0, 1);
-      const uint32_t sQ_addr = smem_u32(sQ), ring_addr = smem_u32(ring);
-      const uint32_t sP_addr = smem_u32(smem + L::kP);
-      auto stage_of = [&](int fill) { return fill % kStages; };
-      auto parity_of = [&](int fill) { return (uint32_t)((fill / kStages) & 1); };
-      auto issue_qk = [&](int x, int j) {
-        const uint32_t a = sQ_addr + x * kTileBytes, b = ring_addr + stage_of(2 * j) * kTileBytes;
+      // high word shared by every operand descriptor here: SBO = 1024 B, version 1, 128-byte swizzle
+      constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (kSw128 << 29);
+      const uint32_t q_lo = (smem_u32(sQ) >> 4) | (1u << 16);                                   // K-major: LBO field = 1
+      const uint32_t ring_k_lo = (smem_u32(ring) >> 4) | (1u << 16);                            // K tile, K-major
+      const uint32_t ring_v_lo = (smem_u32(ring) >> 4) | ((uint32_t)(kHalfBytes >> 4) << 16);   // V tile, MN-major: LBO = half tile
+      auto issue_qk = [&](int x, int stage) {
+        const uint32_t a_lo = q_lo + x * (kTileBytes >> 4), b_lo = ring_k_lo + stage * (kTileBytes >> 4);
+        const uint32_t tS = tmem_base + x * kTileN;
+        umma_ss_f16_lh<0>(tS, a_lo, b_lo, desc_hi, idesc_qk);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ss_f16(tmem_base + x * kTileN, kmajor_desc(a, k), kmajor_desc(b, k), idesc_qk, k > 0);
-      };
-      auto issue_pv = [&](int x, int j) {
-        const uint32_t b = ring_addr + stage_of(2 * j + 1) * kTileBytes;
-        const uint32_t d = tmem_base + 2 * kTileN + x * kHeadDim;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          if constexpr (kPInTmem)
-            umma_ts_f16(d, tmem_base + x * kTileN + k * 8, mnmajor_desc(b, k), idesc_pv, (j > 0) || (k > 0));
-          else
-            umma_ss_f16(d, kmajor_desc(sP_addr + x * kTileBytes, k), mnmajor_desc(b, k), idesc_pv, (j > 0) || (k > 0));
+        for (int k = 1; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * (kHalfBytes >> 4) + (k & 3) * 2;  // 16 k-elements = 32 bytes inside the swizzle row
+          umma_ss_f16_lh<1>(tS, a_lo + off, b_lo + off, desc_hi, idesc_qk);
         }
       };
+      auto issue_pv = [&](int x, int stage, bool first) {
+        const uint32_t b_lo = ring_v_lo + stage * (kTileBytes >> 4);
+        const uint32_t tS = tmem_base + x * kTileN, tO = tmem_base + 2 * kTileN + x * kHeadDim;
+        if (first) umma_ts_f16_lh<0>(tO, tS, b_lo, desc_hi, idesc_pv);
+        else umma_ts_f16_lh<1>(tO, tS, b_lo, desc_hi, idesc_pv);
+#pragma unroll
+        for (int k = 1; k < 8; ++k)  // 16 tokens of V = 2048 bytes; 16 bf16 of P = 8 TMEM columns
+          umma_ts_f16_lh<1>(tO, tS + k * 8, b_lo + k * (2048 >> 4), desc_hi, idesc_pv);
+      };
+      int stage = 0;        // ring stage of the next tile to consume (K_0 first)
+      uint32_t parity = 0;  // its "full" parity
+      auto advance = [&]() {
+        if (++stage == kStages) { stage = 0; parity ^= 1; }
+      };
       bool ok = mbar_wait(q_full, 0, abort_flag);
-      ok = ok && mbar_wait(&kv_full[stage_of(0)], parity_of(0), abort_flag);
+      ok = ok && mbar_wait(&kv_full[stage], parity, abort_flag);
       if (ok) {
         tc_fence_after_sync();
-        issue_qk(0, 0);
+        issue_qk(0, stage);
         umma_commit(&s_full[0]);
-        issue_qk(1, 0);
+        issue_qk(1, stage);
         umma_commit(&s_full[1]);
-        umma_commit(&kv_empty[stage_of(0)]);
+        umma_commit(&kv_empty[stage]);
+        advance();
       }
       for (int j = 0; j < n_tiles && ok; ++j) {
         const bool more = j + 1 < n_tiles;
-        ok = mbar_wait(&kv_full[stage_of(2 * j + 1)], parity_of(2 * j + 1), abort_flag);
-        if (ok && more) ok = mbar_wait(&kv_full[stage_of(2 * j + 2)], parity_of(2 * j + 2), abort_flag);
-        for (int x = 0; x < 2 && ok; ++x) {
+        const int v_stage = stage;
+        ok = mbar_wait(&kv_full[stage], parity, abort_flag);  // V_j
+        advance();
+        const int k_stage = stage;
+        if (ok && more) ok = mbar_wait(&kv_full[stage], parity, abort_flag);  // K_{j+1}
+        if (more) advance();
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (!ok) break;
+          MAGI_STAMP(0, j, 4 * x + 0);
           ok = mbar_wait(&p_full[x], j & 1, abort_flag);
           if (!ok) break;
+          MAGI_STAMP(0, j, 4 * x + 1);
           tc_fence_after_sync();
-          issue_pv(x, j);
+          issue_pv(x, v_stage, j == 0);
           umma_commit(&o_full[x]);
-          if (x == 1) umma_commit(&kv_empty[stage_of(2 * j + 1)]);
+          if (x == 1) umma_commit(&kv_empty[v_stage]);
           if (more) {
-            issue_qk(x, j + 1);
+            issue_qk(x, k_stage);
             umma_commit(&s_full[x]);
-            if (x == 1) umma_commit(&kv_empty[stage_of(2 * j + 2)]);
+            if (x == 1) umma_commit(&kv_empty[k_stage]);
           }
+          MAGI_STAMP(0, j, 4 * x + 2);
         }
       }
     }
@@ -234,84 +284,112 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const Segment sg = pv.segs[sg_i];
       for (int t0 = 0; t0 < sg.len && ok; t0 += kTileN, ++j) {
         const int valid = min(kTileN, sg.len - t0);
+        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 0);
         ok = mbar_wait(&s_full[x], j & 1, abort_flag);
         if (!ok) break;
+        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 1);
         tc_fence_after_sync();
+        // S_x(j) complete implies PV_x(j-1) complete (same issuing thread, in order), so O_x may be rescaled here.
         uint32_t s[kTileN];
-        tmem_ld32(tS, s);
-        tmem_ld32(tS + 32, s + 32);
-        tmem_ld32(tS + 64, s + 64);
-        tmem_ld32(tS + 96, s + 96);
-        tmem_wait_ld();
-        if (valid < kTileN) {
+        auto load_s = [&]() {
+          tmem_ld32(tS, s);
+          tmem_ld32(tS + 32, s + 32);
+          tmem_ld32(tS + 64, s + 64);
+          tmem_ld32(tS + 96, s + 96);
+          tmem_wait_ld();
+          if (valid < kTileN) {
 #pragma unroll
-          for (int c = 0; c < kTileN; ++c)
-            if (c >= valid) s[c] = 0xff800000u;  // -inf
-        }
-        // row maximum with 8 independent chains (a single 127-long dependent chain costs ~500 cycles)
-        float mxa[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) mxa[c] = __uint_as_float(s[c]);
-#pragma unroll
-        for (int c = 8; c < kTileN; ++c) mxa[c & 7] = fmaxf(mxa[c & 7], __uint_as_float(s[c]));
-        const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
-                               fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
-        // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8 larger.
-        const float m_new = fmaxf(m_used, mx);
-        const bool need = (m_new - m_used) * sl2 > 8.0f;
-        const float m_cur = need ? m_new : m_used;
-        const float alpha = need ? ex2((m_used - m_new) * sl2) : 1.0f;
-        const float neg_m = -m_cur * sl2;
-        float rs[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < kTileN; c += 4) {
-          const float p0 = ex2(fmaf(__uint_as_float(s[c]), sl2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), sl2, neg_m));
-          const float p2 = ex2(fmaf(__uint_as_float(s[c + 2]), sl2, neg_m));
-          const float p3 = ex2(fmaf(__uint_as_float(s[c + 3]), sl2, neg_m));
-          rs[0] += p0;
-          rs[1] += p1;
-          rs[2] += p2;
-          rs[3] += p3;
-          s[c >> 1] = pack_bf16x2(p0, p1);
-          s[(c >> 1) + 1] = pack_bf16x2(p2, p3);
-        }
-        const float rowsum0 = rs[0] + rs[2], rowsum1 = rs[1] + rs[3];
-        if constexpr (kPInTmem) {
-          tmem_st32(tS, s);
-          tmem_st32(tS + 32, s + 32);
-        } else {
-          uint8_t* sP = smem + L::kP + x * kTileBytes;
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {  // 16-byte chunk c holds columns 8c..8c+7
-            const int h = c >> 3, cc = c & 7;
-            *reinterpret_cast<uint4*>(sP + h * kHalfBytes + row * 128 + ((cc ^ (row & 7)) << 4)) =
-                make_uint4(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3]);
+            for (int c = 0; c < kTileN; ++c)
+              if (c >= valid) s[c] = 0xff800000u;  // -inf
           }
-        }
+        };
+        load_s();
+        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 2);
+        float alpha = 1.0f, rowsum = 0.f;
+        bool redo = (j == 0);
         if (j > 0) {
-          // O_x of tile j-1 must be complete before it is rescaled and before P_j may be consumed.
-          ok = mbar_wait(&o_full[x], (j - 1) & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after_sync();
-          if (__any_sync(0xffffffffu, need)) {
-#pragma unroll 1
-            for (int c4 = 0; c4 < 4; ++c4) {
-              uint32_t o[32];
-              tmem_ld32(tO + c4 * 32, o);
-              tmem_wait_ld();
+          // Fast path: exponentials against the maximum already baked into O and l, the tile's own maximum computed
+          // alongside (8 + 4 independent chains keep the MUFU pipe fed).  If the maximum turns out to have grown by
+          // more than 2^8 for any row of the warp, the tile is redone below from the S still held in TMEM.
+          const float neg_m = -m_used * sl2;
+          float mxa[8], rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-              tmem_st32(tO + c4 * 32, o);
-            }
+          for (int c = 0; c < 8; ++c) mxa[c] = __uint_as_float(s[c]);
+#pragma unroll
+          for (int c = 0; c < kTileN; c += 4) {
+            const float s0 = __uint_as_float(s[c]), s1 = __uint_as_float(s[c + 1]);
+            const float s2 = __uint_as_float(s[c + 2]), s3 = __uint_as_float(s[c + 3]);
+            mxa[c & 7] = fmaxf(mxa[c & 7], s0);
+            mxa[(c + 1) & 7] = fmaxf(mxa[(c + 1) & 7], s1);
+            mxa[(c + 2) & 7] = fmaxf(mxa[(c + 2) & 7], s2);
+            mxa[(c + 3) & 7] = fmaxf(mxa[(c + 3) & 7], s3);
+            const float p0 = ex2(fmaf(s0, sl2, neg_m)), p1 = ex2(fmaf(s1, sl2, neg_m));
+            const float p2 = ex2(fmaf(s2, sl2, neg_m)), p3 = ex2(fmaf(s3, sl2, neg_m));
+            rs[0] += p0;
+            rs[1] += p1;
+            rs[2] += p2;
+            rs[3] += p3;
+            s[c >> 1] = pack_bf16x2(p0, p1);
+            s[(c >> 1) + 1] = pack_bf16x2(p2, p3);
+          }
+          const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
+                                 fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
+          rowsum = (rs[0] + rs[2]) + (rs[1] + rs[3]);
+          redo = __any_sync(0xffffffffu, (mx - m_used) * sl2 > 8.0f);
+          if (redo) load_s();
+        }
+        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 3);
+        if (redo) {
+          // Exact path (first tile, or the running maximum moved): new reference maximum, then the exponentials.
+          float mxa[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) mxa[c] = __uint_as_float(s[c]);
+#pragma unroll
+          for (int c = 8; c < kTileN; ++c) mxa[c & 7] = fmaxf(mxa[c & 7], __uint_as_float(s[c]));
+          const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
+                                 fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
+          const float m_new = fmaxf(m_used, mx);
+          const bool need = (m_new - m_used) * sl2 > 8.0f;  // rows that did not move keep their reference maximum
+          const float m_cur = need ? m_new : m_used;
+          alpha = need ? ex2((m_used - m_new) * sl2) : 1.0f;
+          const float neg_m = -m_cur * sl2;
+          float rs[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int c = 0; c < kTileN; c += 4) {
+            const float p0 = ex2(fmaf(__uint_as_float(s[c]), sl2, neg_m));
+            const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), sl2, neg_m));
+            const float p2 = ex2(fmaf(__uint_as_float(s[c + 2]), sl2, neg_m));
+            const float p3 = ex2(fmaf(__uint_as_float(s[c + 3]), sl2, neg_m));
+            rs[0] += p0;
+            rs[1] += p1;
+            rs[2] += p2;
+            rs[3] += p3;
+            s[c >> 1] = pack_bf16x2(p0, p1);
+            s[(c >> 1) + 1] = pack_bf16x2(p2, p3);
+          }
+          rowsum = (rs[0] + rs[2]) + (rs[1] + rs[3]);
+          m_used = m_cur;
+        }
+        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 4);
+        tmem_st32(tS, s);
+        tmem_st32(tS + 32, s + 32);
+        if (redo && j > 0) {
+#pragma unroll 1
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint32_t o[32];
+            tmem_ld32(tO + c4 * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+            tmem_st32(tO + c4 * 32, o);
           }
         }
-        l = l * alpha + (rowsum0 + rowsum1);
-        m_used = m_cur;
+        l = l * alpha + rowsum;
+        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 5);
         tmem_wait_st();
-        if constexpr (!kPInTmem) fence_proxy_async_smem();
         tc_fence_before_sync();
         mbar_arrive(&p_full[x]);
+        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 6);
       }
     }
     if (ok) ok = mbar_wait(&o_full[x], (n_tiles - 1) & 1, abort_flag);
@@ -351,6 +429,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
+#ifdef MAGI_TRACE
+  if (threadIdx.x == 0) {
+    long long t1;
+    unsigned smid;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    const int id = blockIdx.y * gridDim.x + blockIdx.x;
+    if (id < 8192) {
+      g_cta_log[id][0] = cta_t0;
+      g_cta_log[id][1] = t1;
+      g_cta_log[id][2] = n_tiles;
+      g_cta_log[id][3] = smid;
+    }
+  }
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------- host side
@@ -389,17 +482,23 @@ int make_tile_map(magi_ctx* ctx, CUtensorMap* m, const void* base, int64_t strid
 }
 
 // Opt in to > 48 KB of dynamic shared memory; called once per context with its device current.
+#ifdef MAGI_TRACE
+extern "C" __attribute__((visibility("default"))) int magi_debug_read_cta_log(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_cta_log, sizeof(g_cta_log));
+}
+extern "C" __attribute__((visibility("default"))) int magi_debug_read_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(g_trace));
+}
+#endif
+
 int attn_fp8_init_device(magi_ctx* ctx);
 int attn_init_device(magi_ctx* ctx) {
   if (int rc = attn_fp8_init_device(ctx)) return rc;
-  MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SmemLayout<true>::kDynamic));
-  MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SmemLayout<false>::kDynamic));
+  MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::kDynamic));
   return MAGI_OK;
 }
 
-int launch_attn_bf16(magi_ctx* ctx, const magi_attn_params* p, int max_items, bool p_in_tmem, cudaStream_t stream) {
+int launch_attn_bf16(magi_ctx* ctx, const magi_attn_params* p, int max_items, cudaStream_t stream) {
   CUtensorMap tq, tk, tv, tkc, tvc;
   int rc;
   if ((rc = make_tile_map(ctx, &tq, p->q, p->q_stride_t, p->q_stride_h, p->total_q, p->n_q_heads, 2, "q"))) return rc;
@@ -432,10 +531,7 @@ int launch_attn_bf16(magi_ctx* ctx, const magi_attn_params* p, int max_items, bo
   kp.scale_log2 = kp.scale * 1.4426950408889634f;
 
   dim3 grid(max_items, p->n_q_heads, 1);
-  if (p_in_tmem)
-    attn_fwd_kernel<true><<<grid, kAttnThreads, SmemLayout<true>::kDynamic, stream>>>(tq, tk, tv, tkc, tvc, kp);
-  else
-    attn_fwd_kernel<false><<<grid, kAttnThreads, SmemLayout<false>::kDynamic, stream>>>(tq, tk, tv, tkc, tvc, kp);
+  attn_fwd_kernel<<<grid, kAttnThreads, SmemLayout::kDynamic, stream>>>(tq, tk, tv, tkc, tvc, kp);
   MAGI_CUDA_OK(ctx, cudaGetLastError());
   return MAGI_OK;
 }
