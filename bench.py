@@ -212,7 +212,7 @@ def main():
     if cp > 1:
         from magi_b200.ulysses import UlyssesAttention
         ua = UlyssesAttention(cp_group=dist.group.WORLD, n_q_heads=Hq, n_kv_heads=Hkv, split_sizes=splits)
-    attn_ev = []
+    attn_ev, prologue_ev = [], []
     n_launch = [0]
 
     def timed_attn(record, fn):
@@ -282,7 +282,13 @@ def main():
 
         def step(record=False):
             if cp == 1:
+                if record:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
                 mb.qk_norm_rope(xq, gq, bq, cos, sin, out=q_buf)
+                if record:
+                    e1.record()
+                    prologue_ev.append((e0, e1))
                 mb.qk_norm_rope(xk, gk, bk, cos, sin, out=k_buf)
                 timed_attn(record, lambda: mb.chunk_attn(q_buf, k_buf, xv, qr, kr, C, S, out=out_buf, return_lse=False))
                 n_launch[0] = 4
@@ -377,6 +383,12 @@ def main():
             "clocks": sampler.summary(),
             "gpu_launches": args.steps * n_launch[0],
         }
+        if prologue_ev:
+            pms = sum(a.elapsed_time(b) for a, b in prologue_ev) / len(prologue_ev)
+            pbytes = 2 * xq.numel() * 2 + 2 * cos.numel() * 4  # bf16 read + bf16 write of Q, cos+sin once
+            line["prologue_q"] = {"kernel": "prologue16_kernel", "bound": "hbm", "ms": pms, "algorithmic_bytes": pbytes,
+                                  "achieved_gbs": pbytes / (pms * 1e-3) / 1e9, "peak_gbs": peaks["hbm"],
+                                  "frac": pbytes / (pms * 1e-3) / 1e9 / peaks["hbm"]}
         if w.get("fp8"):
             fp8_peak = measure_fp8_peak(dev)
             line["roofline"]["fp8_peak_measured_tflops"] = fp8_peak

@@ -3,9 +3,13 @@
 // fp32 upcast, LayerNorm over the 128 channels with weight gamma+1 and bias (:355-357), non-interleaved
 // rotary on the first 2*rot_pairs channels in fp32, one rounding to bf16 at the end.
 //
-// A warp owns one (token, head) row: lane l holds channels 4l..4l+3 (8-byte loads, 256 contiguous bytes per
-// warp).  Rotary partners (c, c+rot_pairs) sit rot_pairs/4 lanes apart and are exchanged with one shuffle.
+// Main kernel (rot_pairs a multiple of 8): a HALF-warp owns one (token, head) row: lane l of 16 holds channels 8l..8l+7
+// (16-byte loads and stores, 256 contiguous bytes per half-warp), so a warp instruction serves two rows; row index
+// arithmetic is 32-bit.  Rotary partners (c, c+rot_pairs) sit rot_pairs/8 lanes apart and are exchanged by shuffles.
+// The generic kernel (4 channels per lane, one row per warp) covers the remaining rot_pairs and the plain strided copy.
 #include <cuda_bf16.h>
+
+#include <initializer_list>
 
 #include "common.cuh"
 
@@ -121,6 +125,122 @@ __global__ void __launch_bounds__(256) prologue_kernel(PrologueKernelParams p) {
   }
 }
 
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+constexpr int kRows16PerIter = 4;  // rows (heads) per half-warp in flight: 1 KB of loads per half-warp
+
+// Work unit of a half-warp: one token x `hg` consecutive heads (hg divides H).  cos/sin of the token are loaded once per
+// unit and reused for its heads; the heads of a token are contiguous rows, so a unit streams hg * 256 contiguous bytes.
+__global__ void __launch_bounds__(256, 4) prologue16_kernel(PrologueKernelParams p, int hg) {
+  const int lane = threadIdx.x & 31;
+  const int l16 = lane & 15;
+  const unsigned hw_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;  // half-warp id
+  const unsigned n_hw = (gridDim.x * blockDim.x) >> 4;
+  const unsigned groups = (unsigned)p.H / (unsigned)hg;
+  const unsigned n_units = (unsigned)p.T * groups;
+  const int d = l16 * 8;
+
+  float g[8], b[8];
+  {
+    const float4 g0 = *reinterpret_cast<const float4*>(p.gamma + d), g1 = *reinterpret_cast<const float4*>(p.gamma + d + 4);
+    g[0] = g0.x + 1.f; g[1] = g0.y + 1.f; g[2] = g0.z + 1.f; g[3] = g0.w + 1.f;
+    g[4] = g1.x + 1.f; g[5] = g1.y + 1.f; g[6] = g1.z + 1.f; g[7] = g1.w + 1.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) b[i] = 0.f;
+    if (p.beta && p.norm_mode == MAGI_NORM_LAYERNORM_1P) {
+      const float4 b0 = *reinterpret_cast<const float4*>(p.beta + d), b1 = *reinterpret_cast<const float4*>(p.beta + d + 4);
+      b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+    }
+  }
+  const int rp8 = p.rot_pairs >> 3;
+  int partner = lane;
+  float sign = 0.f;
+  int cs_off = 0;
+  if (l16 < rp8) { partner = lane + rp8; sign = -1.f; cs_off = d; }
+  else if (l16 < 2 * rp8) { partner = lane - rp8; sign = 1.f; cs_off = d - p.rot_pairs; }
+  const bool layernorm = p.norm_mode == MAGI_NORM_LAYERNORM_1P;
+  const unsigned hpb = (unsigned)p.heads_per_block;
+
+  // both half-warps of a warp run the same number of iterations (shuffles are warp-wide): round the bound up to a pair
+  const unsigned n_units_pad = (n_units + 1u) & ~1u;
+  for (unsigned unit = hw_global; unit < n_units_pad; unit += n_hw) {
+    const bool unit_live = unit < n_units;
+    const unsigned uc = unit_live ? unit : 0u;
+    const unsigned t = uc / groups;
+    const unsigned h0 = (uc - t * groups) * (unsigned)hg;
+    float c[8], sn[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { c[k] = 1.f; sn[k] = 0.f; }
+    if (sign != 0.f) {
+      const float* cp = p.cos + (int64_t)t * p.rot_pairs + cs_off;
+      const float* sp = p.sin + (int64_t)t * p.rot_pairs + cs_off;
+      const float4 c0 = __ldg(reinterpret_cast<const float4*>(cp)), c1 = __ldg(reinterpret_cast<const float4*>(cp + 4));
+      const float4 s0 = __ldg(reinterpret_cast<const float4*>(sp)), s1 = __ldg(reinterpret_cast<const float4*>(sp + 4));
+      c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+      sn[0] = sign * s0.x; sn[1] = sign * s0.y; sn[2] = sign * s0.z; sn[3] = sign * s0.w;
+      sn[4] = sign * s1.x; sn[5] = sign * s1.y; sn[6] = sign * s1.z; sn[7] = sign * s1.w;
+    }
+    const __nv_bfloat16* xrow = p.x + (int64_t)t * p.x_stride_t + d;
+    for (int hb = 0; hb < hg; hb += kRows16PerIter) {
+      uint4 raw[kRows16PerIter];
+#pragma unroll
+      for (int i = 0; i < kRows16PerIter; ++i) {
+        const unsigned h = h0 + min(hb + i, hg - 1);
+        raw[i] = __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)h * p.x_stride_h));
+      }
+#pragma unroll
+      for (int i = 0; i < kRows16PerIter; ++i) {
+        const __nv_bfloat162* pr = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { v[2 * k] = __low2float(pr[k]); v[2 * k + 1] = __high2float(pr[k]); }
+        float y[8];
+        if (layernorm) {
+          const float mean = half_warp_sum(((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]))) * (1.f / kHeadDim);
+          float sq = 0.f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) { v[k] -= mean; sq += v[k] * v[k]; }
+          const float rstd = rsqrtf(half_warp_sum(sq) * (1.f / kHeadDim) + p.eps);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) y[k] = v[k] * rstd * g[k] + b[k];
+        } else {
+          float sq = 0.f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) sq += v[k] * v[k];
+          const float rstd = rsqrtf(half_warp_sum(sq) * (1.f / kHeadDim) + p.eps);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) y[k] = v[k] * rstd * g[k];
+        }
+        if (rp8 > 0) {  // uniform: every lane takes part in the exchange; lanes outside the rotary span keep y (c = 1, sn = 0)
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float o = __shfl_sync(0xffffffffu, y[k], partner);
+            y[k] = y[k] * c[k] + o * sn[k];
+          }
+        }
+        if (unit_live && hb + i < hg) {
+          const unsigned h = h0 + hb + i;
+          uint4 res;
+          __nv_bfloat162 t0 = __floats2bfloat162_rn(y[0], y[1]), t1 = __floats2bfloat162_rn(y[2], y[3]);
+          __nv_bfloat162 t2 = __floats2bfloat162_rn(y[4], y[5]), t3 = __floats2bfloat162_rn(y[6], y[7]);
+          res.x = *reinterpret_cast<const uint32_t*>(&t0);
+          res.y = *reinterpret_cast<const uint32_t*>(&t1);
+          res.z = *reinterpret_cast<const uint32_t*>(&t2);
+          res.w = *reinterpret_cast<const uint32_t*>(&t3);
+          const unsigned blk = hpb > 0 ? h / hpb : 0u;
+          const unsigned hs = hpb > 0 ? h - blk * hpb : h;
+          *reinterpret_cast<uint4*>(p.out + (int64_t)blk * p.out_stride_block + (int64_t)t * p.out_stride_t +
+                                    (int64_t)hs * p.out_stride_h + d) = res;
+        }
+      }
+    }
+  }
+}
+
 static int check_prologue(magi_ctx* ctx, const magi_prologue_params* p, bool norm_rope) {
   if (!ctx) return MAGI_E_BADARG;
   if (!p || p->struct_size != sizeof(magi_prologue_params)) return set_err(ctx, MAGI_E_BADARG, "prologue: bad struct_size");
@@ -172,10 +292,24 @@ static int launch_prologue(magi_ctx* ctx, const magi_prologue_params* p, bool no
   const int64_t want = (rows + 8 * kRowsPerIter - 1) / (8 * kRowsPerIter);
   const int64_t cap = (int64_t)ctx->sm_count * 8;  // 8 x 256 threads resident per SM
   const int blocks = (int)(want < cap ? want : cap);
-  if (norm_rope)
+  // 16-byte path: needs rot_pairs % 8 == 0, no source blocking, 16-byte aligned rows on both sides, < 2^32 rows
+  const bool wide = norm_rope && (p->rot_pairs & 7) == 0 && k.x_heads_per_block == 0 && rows < (1ll << 32) &&
+                    !(reinterpret_cast<uintptr_t>(p->x) & 15) && !(reinterpret_cast<uintptr_t>(p->out) & 15) &&
+                    !(p->x_stride_t & 7) && !(p->x_stride_h & 7) && !(p->out_stride_t & 7) && !(p->out_stride_h & 7) &&
+                    !(p->out_stride_block & 7) && (p->rot_pairs == 0 || !((uintptr_t)p->cos & 15));
+  if (wide) {
+    int hg = 1;  // heads per unit: the largest of 8, 6, 4, 3, 2 that divides H
+    for (int cand : {8, 6, 4, 3, 2})
+      if (p->H % cand == 0) { hg = cand; break; }
+    const int64_t units = rows / hg;
+    const int64_t want16 = (units + 15) / 16;  // 16 half-warps per block
+    const int64_t cap16 = (int64_t)ctx->sm_count * 4 * 4;  // 4 resident blocks per SM, x4 waves for balance
+    prologue16_kernel<<<(int)(want16 < cap16 ? want16 : cap16), 256, 0, stream>>>(k, hg);
+  } else if (norm_rope) {
     prologue_kernel<true><<<blocks, 256, 0, stream>>>(k);
-  else
+  } else {
     prologue_kernel<false><<<blocks, 256, 0, stream>>>(k);
+  }
   MAGI_CUDA_OK(ctx, cudaGetLastError());
   return MAGI_OK;
 }
