@@ -95,9 +95,13 @@ class UlyssesAttention:
 
     def forward(self, xq, xk, xv, gq, bq, gk, bk, cos, sin, q_ranges, k_ranges, max_seqlen_q, max_seqlen_k,
                 eps: float = 1e-6, norm_mode: str = "layernorm_1p", cache=None, layer: int = 0,
-                prefix_chunk_ids: Sequence[int] = (), k_range_offsets=None, attn_events: Optional[list] = None):
+                prefix_chunk_ids: Sequence[int] = (), k_range_offsets=None, attn_events: Optional[list] = None,
+                fp8_chunk_tokens: int = 0):
         """xq [s_local, Hq, 128], xk / xv [s_local, Hkv, 128]: this rank's tokens, all heads (projection outputs).
         cos / sin: this rank's rows of the rotary table.  Ranges are in full-sequence token coordinates.
+        fp8_chunk_tokens > 0 runs the FP8 e4m3 attention: the head-sharded Q/K/V are block-quantised after the exchange
+        (scale blocks counted from each multiple of fp8_chunk_tokens; Q and P carried as two terms), the exchange itself
+        and the output stay bf16.
         Returns O [s_local, Hq, 128] for this rank's tokens, heads in global order."""
         ops, ex = self.ops, self.ex
         cp, s_loc, S = ex.cp, ex.s_local, ex.s_total
@@ -114,6 +118,11 @@ class UlyssesAttention:
         q_recv, w_q = ex.scatter_heads(q_send, self._buf("q_recv", (S, self.hq_loc, HEAD_DIM), dev))
         w_kv.wait()
         k_full, v_full = kv_recv[..., :HEAD_DIM], kv_recv[..., HEAD_DIM:]
+        fp8 = {}
+        if fp8_chunk_tokens > 0:
+            k_full, ks = ops.quantize_e4m3(k_full, fp8_chunk_tokens)
+            v_full, vs = ops.quantize_e4m3(v_full, fp8_chunk_tokens)
+            fp8 = dict(k_scale=ks, v_scale=vs, scale_chunk_tokens=fp8_chunk_tokens)
         w_q.wait()
 
         out = self._buf("out", (s_loc, self.hq, HEAD_DIM), dev)
@@ -126,11 +135,14 @@ class UlyssesAttention:
         for i in range(self.overlap):
             # head group i: sub-heads [i*gsub, (i+1)*gsub) of every local KV head (GQA-aware split, context_parallel.py:570-578)
             qi = q_grp[:, :, i * gsub:(i + 1) * gsub].reshape(S, self.hkv_loc * gsub, HEAD_DIM) if self.overlap > 1 else q_recv
+            if fp8_chunk_tokens > 0:
+                qi, qs, q_lo = ops.quantize_e4m3(qi, fp8_chunk_tokens, residual=True)
+                fp8.update(q_scale=qs, q_lo=q_lo)
             if attn_events is not None:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
             ops.chunk_attn(qi, k_full, v_full, q_ranges, k_ranges, max_seqlen_q, max_seqlen_k, out=o_full[i], return_lse=False,
-                           k_range_offsets=k_range_offsets, cache=cache, layer=layer, prefix_chunk_ids=prefix_chunk_ids)
+                           k_range_offsets=k_range_offsets, cache=cache, layer=layer, prefix_chunk_ids=prefix_chunk_ids, **fp8)
             if attn_events is not None:
                 e1.record()
                 attn_events.append((e0, e1))

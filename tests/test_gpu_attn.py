@@ -203,3 +203,40 @@ def test_cfg1_shape_sampled_rows_and_properties(mb):
     out3, _ = mb.chunk_attn(q, k, ones, qr, kr, C, S)
     torch.cuda.synchronize()
     assert (out3.float() - 1).abs().max().item() <= 2 ** -7
+
+
+def test_cfg2_shape_paged_decode_sampled_rows(mb):
+    """The KV-cache decode benchmark shape: batch 2 x 4 denoising chunks of 9360 tokens, 24/8 heads; chunk i of batch
+    element e attends to its own cached clean prefix (i chunks, read in place from bf16 pages) plus itself."""
+    from magi_b200 import host
+    C, n, B, NP, Hq, Hkv = 9360, 4, 2, 3, 24, 8
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn(B * n * C, Hq, 128, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    k = torch.randn(B * n * C, Hkv, 128, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    v = torch.randn(B * n * C, Hkv, 128, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    pages = [torch.randn(C, Hkv, 256, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16) for _ in range(B * NP)]
+    cache = mb.ChunkPagedKVCache(n_layers=1, max_chunks=B * NP, chunk_tokens=C, n_kv_heads=Hkv)
+    order = [4, 0, 5, 2, 1, 3]                       # pages filled out of order: slot != chunk id
+    for cid in order:
+        cache.append_kv(0, cid, pages[cid])
+    qr = host.q_ranges_for_chunks(n, C, batch=B)
+    kr, ko = host.own_prefix_k_segments(n, C, NP, batch=B)
+    out, lse = mb.chunk_attn(q, k, v, qr, kr, C, (NP + 1) * C, k_range_offsets=ko, cache=cache, layer=0,
+                             prefix_chunk_ids=list(range(B * NP)))
+    torch.cuda.synchronize()
+    assert mb.Context.get().status() == 0
+    # oracle on sampled rows over the materialised (prefix | current) key space
+    kv_all = torch.cat(pages).float().cpu()
+    k_virt = torch.cat([kv_all[..., :128], k.float().cpu()])
+    v_virt = torch.cat([kv_all[..., 128:], v.float().cpu()])
+    gen = torch.Generator().manual_seed(3)
+    rows = torch.cat([torch.tensor([0, C - 1, C, 2 * C + 5, 4 * C - 1, 4 * C, 5 * C + 77, 8 * C - 1]),
+                      torch.randint(0, B * n * C, (24,), generator=gen)]).unique()
+    keep, ref, ref_lse = oracle_on_rows(q.float().cpu(), k_virt, v_virt, qr, as_segments(kr, ko), rows)
+    assert_close(out[keep.cuda()], ref, what="cfg2 sampled rows")
+    assert torch.allclose(lse[keep.cuda()].cpu(), ref_lse, atol=3e-3, rtol=1e-3)
+    # chunk 0 of each batch element sees only itself: identical to a plain self-attention over that chunk
+    solo, _ = mb.chunk_attn(q[:C], k[:C], v[:C], np.array([[0, C]], dtype=np.int32), np.array([[0, C]], dtype=np.int32), C, C)
+    torch.cuda.synchronize()
+    assert torch.equal(solo, out[:C])
+    cache.close()
