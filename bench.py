@@ -206,8 +206,7 @@ def main():
     qr = torch.as_tensor(host.q_ranges_for_chunks(n, C), device=dev)
     kr = torch.as_tensor(host.default_k_ranges(n, C), device=dev)
 
-    special = w.get("decode") or w.get("fp8")
-    if special and cp > 1:
+    if w.get("decode") and cp > 1:
         raise SystemExit(f"workload {args.workload} is a single-GPU benchmark line")
     if cp > 1:
         from magi_b200.ulysses import UlyssesAttention
@@ -251,7 +250,7 @@ def main():
                                                      return_lse=False, cache=cache, layer=0, prefix_chunk_ids=list(range(B * NP))))
             n_launch[0] = 4
             return out_buf
-    elif w.get("fp8"):
+    elif w.get("fp8") and cp == 1:
         # ---- cfg 4: fp8; K/V of chunks 0..n-2 sit in an fp8 page cache, the last chunk is fresh
         cache = mb.ChunkPagedKVCache(n_layers=1, max_chunks=n - 1, chunk_tokens=C, n_kv_heads=Hkv, dtype="fp8", device=local_rank)
         k_all = mb.qk_norm_rope(xk, gk, bk, cos, sin)
@@ -293,8 +292,10 @@ def main():
                 timed_attn(record, lambda: mb.chunk_attn(q_buf, k_buf, xv, qr, kr, C, S, out=out_buf, return_lse=False))
                 n_launch[0] = 4
                 return out_buf
-            n_launch[0] = 7
-            return ua.forward(xq, xk, xv, gq, bq, gk, bk, cos, sin, qr, kr, C, S, attn_events=attn_ev if record else None)
+            n_launch[0] = 11 if w.get("fp8") else 7
+            # FP8 under context parallelism: all chunks are fresh (the head-sharded Q/K/V are quantised after the exchange)
+            return ua.forward(xq, xk, xv, gq, bq, gk, bk, cos, sin, qr, kr, C, S, attn_events=attn_ev if record else None,
+                              fp8_chunk_tokens=C if w.get("fp8") else 0)
 
     def barrier():
         if cp > 1:
