@@ -164,6 +164,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: Ulysses exchange fused into the kernels over peer memory, or NCCL all-to-all + copies")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -208,9 +210,11 @@ def main():
 
     if w.get("decode") and cp > 1:
         raise SystemExit(f"workload {args.workload} is a single-GPU benchmark line")
+    fused = cp > 1 and args.exchange == "fused" and not w.get("fp8")
     if cp > 1:
-        from magi_b200.ulysses import UlyssesAttention
-        ua = UlyssesAttention(cp_group=dist.group.WORLD, n_q_heads=Hq, n_kv_heads=Hkv, split_sizes=splits)
+        from magi_b200.ulysses import FusedUlyssesAttention, UlyssesAttention
+        ua = FusedUlyssesAttention(dist.group.WORLD, Hq, Hkv, splits) if fused else \
+            UlyssesAttention(cp_group=dist.group.WORLD, n_q_heads=Hq, n_kv_heads=Hkv, split_sizes=splits)
     attn_ev, prologue_ev = [], []
     n_launch = [0]
 
@@ -292,7 +296,9 @@ def main():
                 timed_attn(record, lambda: mb.chunk_attn(q_buf, k_buf, xv, qr, kr, C, S, out=out_buf, return_lse=False))
                 n_launch[0] = 4
                 return out_buf
-            n_launch[0] = 11 if w.get("fp8") else 7
+            n_launch[0] = 11 if w.get("fp8") else (5 if fused else 7)
+            if fused:
+                return ua.forward(xq, xk, xv, gq, bq, gk, bk, cos, sin, qr, kr, C, S, attn_events=attn_ev if record else None)
             # FP8 under context parallelism: all chunks are fresh (the head-sharded Q/K/V are quantised after the exchange)
             return ua.forward(xq, xk, xv, gq, bq, gk, bk, cos, sin, qr, kr, C, S, attn_events=attn_ev if record else None,
                               fp8_chunk_tokens=C if w.get("fp8") else 0)
@@ -372,7 +378,7 @@ def main():
             "n_gpus": cp, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3" if w.get("fp8") else "bf16", "data": "synthetic",
             "config": {"workload": w["name"], "chunk_tokens": C, "useful_tflop_per_step": flops / 1e12,
-                       "parallelism": f"ulysses-cp{cp}" if cp > 1 else "single-gpu",
+                       "parallelism": (f"ulysses-cp{cp}, exchange " + ("fused into kernels over peer memory" if fused else "NCCL all-to-all")) if cp > 1 else "single-gpu",
                        "l2": "inputs (>= 0.6 GB per step) exceed the 126 MB L2; no explicit flush",
                        "step": "qk layernorm+rope prologue, attention" + (", all-to-all in/out" if cp > 1 else "")},
             "attn_ms": attn_ms,

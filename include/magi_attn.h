@@ -86,6 +86,11 @@ typedef struct {
                                 + t*out_stride_t + (h % heads_per_block)*out_stride_h + d         */
   int64_t out_stride_t, out_stride_h, out_stride_block;
   int32_t heads_per_block;   /* 0 or >= H: no blocking */
+  /* Optional: one destination base per block instead of out + block*out_stride_block (HOST array of
+     H / heads_per_block device pointers, at most 16).  With peer-mapped pointers (magi_peer_open) the prologue
+     writes each context-parallel rank's share of the heads straight into that rank's receive buffer over NVLink:
+     the "scatter heads" all-to-all of context_parallel.py:381-401 fused into its producer. */
+  void* const* out_block_ptrs;
   int32_t x_heads_per_block; /* source blocking (the inverse re-layout "(cp sq) hn hd -> sq (cp hn) hd" after the
                                 output all-to-all, context_parallel.py:596): element (t,h,d) is read at
                                 x + (h / x_heads_per_block)*x_stride_block + t*x_stride_t + (h % x_heads_per_block)*x_stride_h + d.
@@ -184,6 +189,15 @@ typedef struct {
    * When given, the kernel runs its two-term mode: S = (Q8 + Q8_lo) K8^T and O += (P8 + P8_lo) V8, which removes the
    * quantisation noise of Q and of P (K and V stay single e4m3) at the price of twice the UMMA work. */
   const void* q_lo;
+  /* Optional fused output exchange (the "gather heads" all-to-all of context_parallel.py:404-423 and the final
+   * "(cp sq) hn hd -> sq (cp hn) hd" re-layout at :596, fused into the attention epilogue): q row t belongs to the
+   * context-parallel rank d with o_peer_offsets[d] <= t < o_peer_offsets[d+1] and is stored at
+   * o_peer_ptrs[d] + (t - o_peer_offsets[d]) * o_stride_t + (o_head_offset + head) * o_stride_h, with plain stores
+   * (peer-mapped pointers from magi_peer_open for d != own rank).  `out` is then ignored.  HOST arrays, n_o_peers <= 16. */
+  void* const* o_peer_ptrs;
+  const int32_t* o_peer_offsets;   /* [n_o_peers + 1] */
+  int32_t n_o_peers;
+  int32_t o_head_offset;
 } magi_attn_params;
 MAGI_API int magi_chunk_attn_fwd(magi_ctx* ctx, const magi_attn_params* p, void* stream);
 /* Diagnostic twin: same plan, same arguments (bf16 only), plain CUDA-core arithmetic in fp32.  It exists so a
@@ -208,6 +222,15 @@ MAGI_API int magi_chunk_attn_fwd_simt(magi_ctx* ctx, const magi_attn_params* p, 
  *     (0, MAGI_E_RANGE or MAGI_E_TIMEOUT).  err/err_len (host buffer, may be NULL/0) receives the failure text. */
 MAGI_API int magi_chunk_attn_fwd_noalloc(const magi_attn_params* p, void* stream, int32_t* status_dev, char* err,
                                          int err_len);
+
+/* Peer-visible device buffers for the fused Ulysses exchange: cudaMalloc + CUDA IPC (plain peer loads / stores over
+ * NVLink; no multicast object is created).  magi_peer_alloc returns the local pointer and a 64-byte handle to hand to
+ * the other ranks of the box (e.g. through torch.distributed all_gather_object); magi_peer_open maps a peer's handle.
+ * No reference counterpart (the reference moves the data with NCCL all_to_all_single, context_parallel.py:398,420). */
+MAGI_API int magi_peer_alloc(magi_ctx* ctx, uint64_t bytes, void** dev_ptr, unsigned char handle_out[64]);
+MAGI_API int magi_peer_open(magi_ctx* ctx, const unsigned char handle[64], void** dev_ptr);
+MAGI_API int magi_peer_close(magi_ctx* ctx, void* dev_ptr);
+MAGI_API int magi_peer_free(magi_ctx* ctx, void* dev_ptr);
 
 /* bf16 [T,H,128] -> e4m3 [T,H,128] + fp32 scales [n_blocks,H] (scale = absmax/448 per (128-token block, head),
  * blocks counted from each multiple of chunk_tokens).  x8_lo (optional, same shape) receives the e4m3 rounding

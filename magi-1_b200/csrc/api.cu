@@ -267,11 +267,62 @@ extern "C" int magi_kv_cache_read(magi_kv_cache* c, int layer, int chunk_id, voi
   return MAGI_OK;
 }
 
+// ------------------------------------------------------------------------------------------- peer buffers (CUDA IPC)
+extern "C" int magi_peer_alloc(magi_ctx* ctx, uint64_t bytes, void** dev_ptr, unsigned char handle_out[64]) {
+  if (!ctx || !dev_ptr || !handle_out || bytes == 0) return set_err(ctx, MAGI_E_BADARG, "peer alloc: bad argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(ctx->device);
+  void* ptr = nullptr;
+  cudaError_t e = cudaMalloc(&ptr, bytes);
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, ptr);
+  cudaSetDevice(prev);
+  if (e != cudaSuccess) {
+    if (ptr) cudaFree(ptr);
+    cudaGetLastError();
+    return set_err(ctx, e == cudaErrorMemoryAllocation ? MAGI_E_NOMEM : MAGI_E_CUDA, "peer alloc of %llu bytes: %s",
+                   (unsigned long long)bytes, cudaGetErrorString(e));
+  }
+  memcpy(handle_out, &h, 64);
+  *dev_ptr = ptr;
+  return MAGI_OK;
+}
+
+extern "C" int magi_peer_open(magi_ctx* ctx, const unsigned char handle[64], void** dev_ptr) {
+  if (!ctx || !handle || !dev_ptr) return set_err(ctx, MAGI_E_BADARG, "peer open: bad argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(ctx->device);
+  cudaError_t e = cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  cudaSetDevice(prev);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return set_err(ctx, MAGI_E_CUDA, "peer open: %s", cudaGetErrorString(e));
+  }
+  return MAGI_OK;
+}
+
+extern "C" int magi_peer_close(magi_ctx* ctx, void* dev_ptr) {
+  if (!ctx || !dev_ptr) return set_err(ctx, MAGI_E_BADARG, "peer close: bad argument");
+  MAGI_CUDA_OK(ctx, cudaIpcCloseMemHandle(dev_ptr));
+  return MAGI_OK;
+}
+
+extern "C" int magi_peer_free(magi_ctx* ctx, void* dev_ptr) {
+  if (!ctx || !dev_ptr) return set_err(ctx, MAGI_E_BADARG, "peer free: bad argument");
+  MAGI_CUDA_OK(ctx, cudaFree(dev_ptr));
+  return MAGI_OK;
+}
+
 // ------------------------------------------------------------------------------------------- attention
 static int attn_common(magi_ctx* ctx, const magi_attn_params* p, void* stream, int impl) {
   if (!ctx) return MAGI_E_BADARG;
   if (!p || p->struct_size != sizeof(magi_attn_params)) return set_err(ctx, MAGI_E_BADARG, "attn: bad struct_size");
-  if (!p->q || !p->out || !p->q_ranges || !p->k_ranges) return set_err(ctx, MAGI_E_BADARG, "attn: null q/out/ranges");
+  if (!p->q || (!p->out && p->n_o_peers == 0) || !p->q_ranges || !p->k_ranges) return set_err(ctx, MAGI_E_BADARG, "attn: null q/out/ranges");
   if (p->total_q <= 0 || p->total_k < 0 || p->n_q_heads <= 0 || p->n_kv_heads <= 0 || p->n_ranges <= 0 ||
       p->n_k_ranges <= 0 || p->max_seqlen_q <= 0)
     return set_err(ctx, MAGI_E_BADARG, "attn: sizes must be positive");
@@ -283,6 +334,15 @@ static int attn_common(magi_ctx* ctx, const magi_attn_params* p, void* stream, i
   if (p->n_q_heads > 65535) return set_err(ctx, MAGI_E_BADARG, "attn: too many heads");
   if ((reinterpret_cast<uintptr_t>(p->out) & 15) || (p->o_stride_t & 7) || (p->o_stride_h & 7))
     return set_err(ctx, MAGI_E_ALIGN, "attn: out must be 16-byte aligned with strides multiple of 8 elements");
+  if (p->n_o_peers != 0) {
+    if (p->n_o_peers < 0 || p->n_o_peers > 16 || !p->o_peer_ptrs || !p->o_peer_offsets || impl == 2 || p->lse)
+      return set_err(ctx, MAGI_E_BADARG, "attn: fused output exchange needs 1..16 peers, pointer and offset tables, no lse, tensor-core kernel");
+    if (p->o_peer_offsets[0] != 0 || p->o_peer_offsets[p->n_o_peers] != p->total_q)
+      return set_err(ctx, MAGI_E_RANGE, "attn: o_peer_offsets must run from 0 to total_q");
+    for (int i = 0; i < p->n_o_peers; ++i)
+      if (!p->o_peer_ptrs[i] || (reinterpret_cast<uintptr_t>(p->o_peer_ptrs[i]) & 15) || p->o_peer_offsets[i + 1] < p->o_peer_offsets[i])
+        return set_err(ctx, MAGI_E_BADARG, "attn: bad o_peer table entry %d", i);
+  }
   if (p->dtype != MAGI_DTYPE_BF16 && p->dtype != MAGI_DTYPE_FP8_E4M3) return set_err(ctx, MAGI_E_BADARG, "attn: unknown dtype");
   const bool fp8 = p->dtype == MAGI_DTYPE_FP8_E4M3;
   if (fp8 && impl == 2) return set_err(ctx, MAGI_E_BADARG, "attn: the diagnostic kernel is bf16 only");

@@ -36,6 +36,11 @@ struct AttnKernelParams {
   int group;          // q heads per kv head
   float scale;        // softmax scale
   float scale_log2;   // scale * log2(e)
+  // fused output exchange: rank d owns q rows [peer_off[d], peer_off[d+1]) and receives them at peer_out[d]
+  int n_peers;        // 0: plain output to `out`
+  int head_offset;
+  int peer_off[17];
+  __nv_bfloat16* peer_out[16];
 };
 
 // Optional device-side timeline (compiled only with -DMAGI_TRACE, never in the shipped library): CTA (0,0) stamps
@@ -398,22 +403,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int r_in_item = x * kTileM + row;
       const bool valid_row = r_in_item < it.q_rows;
       const float inv = 1.0f / l;
-      __nv_bfloat16* dst = p.out + (int64_t)(it.q_row0 + r_in_item) * p.o_stride_t + (int64_t)head * p.o_stride_h;
+      // Stage the warp's 32 rows x 256 B through the (now idle) shared memory of its own Q tile, so that the global
+      // stores are whole 256-byte rows per half-warp instead of 16-byte pieces of 32 different rows; this matters when
+      // the destination is a peer GPU (NVLink packets) and costs nothing locally.  16-byte chunks are XOR-swizzled
+      // by the row index: conflict-free in both directions.
+      uint8_t* stage = sQ + x * kTileBytes + quarter * (32 * 256);
 #pragma unroll 1
       for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t o[32];
         tmem_ld32(tO + c4 * 32, o);
         tmem_wait_ld();
-        if (valid_row) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(o[8 * c + 0]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
-            v.y = pack_bf16x2(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
-            v.z = pack_bf16x2(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
-            v.w = pack_bf16x2(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c4 * 32 + c * 8) = v;
+        for (int c = 0; c < 4; ++c) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(o[8 * c + 0]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
+          v.y = pack_bf16x2(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
+          v.z = pack_bf16x2(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
+          v.w = pack_bf16x2(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
+          *reinterpret_cast<uint4*>(stage + lane * 256 + (((c4 * 4 + c) ^ (lane & 15)) << 4)) = v;
+        }
+      }
+      __syncwarp();
+      const int l16 = lane & 15, hsel = lane >> 4;
+#pragma unroll 4
+      for (int i = 0; i < 16; ++i) {
+        const int rr = 2 * i + hsel;                       // row inside this warp's 32
+        const int r_item = x * kTileM + quarter * 32 + rr;  // row inside the work item
+        if (r_item < it.q_rows) {
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 256 + (l16 << 4));
+          const int t = it.q_row0 + r_item;
+          __nv_bfloat16* dst_row;
+          if (p.n_peers > 0) {  // the row goes to the rank that owns this token, at this rank's global head position
+            int d = 0;
+            while (d + 1 < p.n_peers && t >= p.peer_off[d + 1]) ++d;
+            dst_row = p.peer_out[d] + (int64_t)(t - p.peer_off[d]) * p.o_stride_t + (int64_t)(p.head_offset + head) * p.o_stride_h;
+          } else {
+            dst_row = p.out + (int64_t)t * p.o_stride_t + (int64_t)head * p.o_stride_h;
           }
+          *reinterpret_cast<uint4*>(dst_row + ((l16 ^ (rr & 15)) << 3)) = v;
         }
       }
       if (p.lse && valid_row)
@@ -529,6 +556,10 @@ int launch_attn_bf16(magi_ctx* ctx, const magi_attn_params* p, int max_items, cu
   kp.group = p->n_q_heads / p->n_kv_heads;
   kp.scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / sqrtf((float)kHeadDim);
   kp.scale_log2 = kp.scale * 1.4426950408889634f;
+  kp.n_peers = p->n_o_peers;
+  kp.head_offset = p->o_head_offset;
+  for (int i = 0; i < 17; ++i) kp.peer_off[i] = i <= p->n_o_peers && p->n_o_peers > 0 ? p->o_peer_offsets[i] : 0;
+  for (int i = 0; i < 16; ++i) kp.peer_out[i] = i < p->n_o_peers ? reinterpret_cast<__nv_bfloat16*>(p->o_peer_ptrs[i]) : nullptr;
 
   dim3 grid(max_items, p->n_q_heads, 1);
   attn_fwd_kernel<<<grid, kAttnThreads, SmemLayout::kDynamic, stream>>>(tq, tk, tv, tkc, tvc, kp);

@@ -30,6 +30,8 @@ struct PrologueKernelParams {
   __nv_bfloat16* out;
   int64_t out_stride_t, out_stride_h, out_stride_block;
   int heads_per_block;
+  int use_block_ptrs;              // destination base of block b is out_blocks[b] instead of out + b * out_stride_block
+  __nv_bfloat16* out_blocks[16];
 };
 
 constexpr int kRowsPerIter = 4;
@@ -119,8 +121,8 @@ __global__ void __launch_bounds__(256) prologue_kernel(PrologueKernelParams p) {
       }
       const int blk = p.heads_per_block > 0 ? hh[i] / p.heads_per_block : 0;
       const int hs = p.heads_per_block > 0 ? hh[i] - blk * p.heads_per_block : hh[i];
-      *reinterpret_cast<uint2*>(p.out + (int64_t)blk * p.out_stride_block + (int64_t)tt[i] * p.out_stride_t +
-                                (int64_t)hs * p.out_stride_h + d) = res;
+      __nv_bfloat16* ob = p.use_block_ptrs ? p.out_blocks[blk] : p.out + (int64_t)blk * p.out_stride_block;
+      *reinterpret_cast<uint2*>(ob + (int64_t)tt[i] * p.out_stride_t + (int64_t)hs * p.out_stride_h + d) = res;
     }
   }
 }
@@ -233,8 +235,8 @@ __global__ void __launch_bounds__(256, 4) prologue16_kernel(PrologueKernelParams
           res.w = *reinterpret_cast<const uint32_t*>(&t3);
           const unsigned blk = hpb > 0 ? h / hpb : 0u;
           const unsigned hs = hpb > 0 ? h - blk * hpb : h;
-          *reinterpret_cast<uint4*>(p.out + (int64_t)blk * p.out_stride_block + (int64_t)t * p.out_stride_t +
-                                    (int64_t)hs * p.out_stride_h + d) = res;
+          __nv_bfloat16* ob = p.use_block_ptrs ? p.out_blocks[blk] : p.out + (int64_t)blk * p.out_stride_block;
+          *reinterpret_cast<uint4*>(ob + (int64_t)t * p.out_stride_t + (int64_t)hs * p.out_stride_h + d) = res;
         }
       }
     }
@@ -244,7 +246,15 @@ __global__ void __launch_bounds__(256, 4) prologue16_kernel(PrologueKernelParams
 static int check_prologue(magi_ctx* ctx, const magi_prologue_params* p, bool norm_rope) {
   if (!ctx) return MAGI_E_BADARG;
   if (!p || p->struct_size != sizeof(magi_prologue_params)) return set_err(ctx, MAGI_E_BADARG, "prologue: bad struct_size");
-  if (!p->x || !p->out || p->T < 0 || p->H <= 0) return set_err(ctx, MAGI_E_BADARG, "prologue: null tensor or bad shape");
+  if (!p->x || (!p->out && !p->out_block_ptrs) || p->T < 0 || p->H <= 0)
+    return set_err(ctx, MAGI_E_BADARG, "prologue: null tensor or bad shape");
+  if (p->out_block_ptrs) {
+    if (p->heads_per_block <= 0 || p->H % p->heads_per_block || p->H / p->heads_per_block > 16)
+      return set_err(ctx, MAGI_E_BADARG, "prologue: out_block_ptrs needs heads_per_block dividing H into at most 16 blocks");
+    for (int b = 0; b < p->H / p->heads_per_block; ++b)
+      if (!p->out_block_ptrs[b] || (reinterpret_cast<uintptr_t>(p->out_block_ptrs[b]) & 15))
+        return set_err(ctx, MAGI_E_ALIGN, "prologue: out_block_ptrs[%d] is null or not 16-byte aligned", b);
+  }
   if ((reinterpret_cast<uintptr_t>(p->x) & 7) || (reinterpret_cast<uintptr_t>(p->out) & 7) || (p->x_stride_t & 3) ||
       (p->x_stride_h & 3) || (p->x_stride_block & 3) || (p->out_stride_t & 3) || (p->out_stride_h & 3) ||
       (p->out_stride_block & 3))
@@ -287,7 +297,10 @@ static int launch_prologue(magi_ctx* ctx, const magi_prologue_params* p, bool no
   k.out_stride_t = p->out_stride_t;
   k.out_stride_h = p->out_stride_h;
   k.out_stride_block = p->out_stride_block;
-  k.heads_per_block = (p->heads_per_block > 0 && p->heads_per_block < p->H) ? p->heads_per_block : 0;
+  k.heads_per_block = (p->heads_per_block > 0 && (p->heads_per_block < p->H || p->out_block_ptrs)) ? p->heads_per_block : 0;
+  k.use_block_ptrs = p->out_block_ptrs ? 1 : 0;
+  for (int b = 0; b < 16; ++b)
+    k.out_blocks[b] = (p->out_block_ptrs && b < p->H / p->heads_per_block) ? reinterpret_cast<__nv_bfloat16*>(p->out_block_ptrs[b]) : nullptr;
   const int64_t rows = (int64_t)p->T * p->H;
   const int64_t want = (rows + 8 * kRowsPerIter - 1) / (8 * kRowsPerIter);
   const int64_t cap = (int64_t)ctx->sm_count * 8;  // 8 x 256 threads resident per SM

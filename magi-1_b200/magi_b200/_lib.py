@@ -18,6 +18,7 @@ EXPORTS = [
     "magi_qk_norm_rope_fwd", "magi_head_block_copy", "magi_kv_cache_create", "magi_kv_cache_destroy",
     "magi_kv_cache_append", "magi_kv_cache_evict", "magi_kv_cache_read", "magi_kv_cache_bytes",
     "magi_chunk_attn_fwd", "magi_chunk_attn_fwd_simt", "magi_quantize_e4m3_block128", "magi_chunk_attn_fwd_noalloc",
+    "magi_peer_alloc", "magi_peer_open", "magi_peer_close", "magi_peer_free",
 ]
 
 
@@ -29,7 +30,8 @@ class PrologueParams(C.Structure):
         ("gamma", C.c_void_p), ("beta", C.c_void_p), ("eps", C.c_float), ("rot_pairs", C.c_int32),
         ("cos", C.c_void_p), ("sin", C.c_void_p),
         ("out", C.c_void_p), ("out_stride_t", C.c_int64), ("out_stride_h", C.c_int64), ("out_stride_block", C.c_int64),
-        ("heads_per_block", C.c_int32), ("x_heads_per_block", C.c_int32), ("x_stride_block", C.c_int64),
+        ("heads_per_block", C.c_int32), ("out_block_ptrs", C.POINTER(C.c_void_p)),
+        ("x_heads_per_block", C.c_int32), ("x_stride_block", C.c_int64),
     ]
 
 
@@ -56,6 +58,8 @@ class AttnParams(C.Structure):
         ("prefix_chunk_ids", C.POINTER(C.c_int32)),
         ("q_scale", C.c_void_p), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
         ("scale_chunk_tokens", C.c_int32), ("reserved", C.c_int32), ("q_lo", C.c_void_p),
+        ("o_peer_ptrs", C.POINTER(C.c_void_p)), ("o_peer_offsets", C.POINTER(C.c_int32)),
+        ("n_o_peers", C.c_int32), ("o_head_offset", C.c_int32),
     ]
 
 
@@ -84,6 +88,10 @@ def _load():
         "magi_chunk_attn_fwd_simt": (C.c_int, [vp, C.POINTER(AttnParams), vp]),
         "magi_quantize_e4m3_block128": (C.c_int, [vp, vp, i64, i64, i32, i32, i32, vp, vp, vp, vp]),
         "magi_chunk_attn_fwd_noalloc": (C.c_int, [C.POINTER(AttnParams), vp, vp, C.c_char_p, i32]),
+        "magi_peer_alloc": (C.c_int, [vp, C.c_uint64, C.POINTER(vp), C.c_char_p]),
+        "magi_peer_open": (C.c_int, [vp, C.c_char_p, C.POINTER(vp)]),
+        "magi_peer_close": (C.c_int, [vp, vp]),
+        "magi_peer_free": (C.c_int, [vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -76,8 +76,11 @@ def _ranges_dev(r, device) -> torch.Tensor:
 
 def qk_norm_rope(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor], cos: Optional[torch.Tensor],
                  sin: Optional[torch.Tensor], eps: float = 1e-6, norm_mode: str = "layernorm_1p",
-                 out: Optional[torch.Tensor] = None, heads_per_block: int = 0, stream=None) -> torch.Tensor:
+                 out: Optional[torch.Tensor] = None, heads_per_block: int = 0, stream=None, block_out=None) -> torch.Tensor:
     """x bf16 [T,H,128] (any token/head strides) -> bf16 normed + rotated.
+
+    block_out = (ptrs, stride_t, stride_h): one raw destination base address per head block (peer-mapped receive
+    buffers of the context-parallel ranks) instead of `out`; heads_per_block is then required.
 
     out=None gives the packed [T,H,128].  With heads_per_block = H/cp and out = [cp, T, H/cp, 128] the result
     is the Ulysses send layout "(cp seq) hn hd" written directly.
@@ -85,7 +88,7 @@ def qk_norm_rope(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tens
     _thd(x, "x")
     T, H, _ = x.shape
     ctx = Context.get(x.device)
-    if out is None:
+    if out is None and block_out is None:
         out = torch.empty(T, H, HEAD_DIM, dtype=torch.bfloat16, device=x.device)
     p = PrologueParams()
     p.struct_size = C.sizeof(PrologueParams)
@@ -102,12 +105,13 @@ def qk_norm_rope(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tens
         sin = sin.to(device=x.device, dtype=torch.float32).contiguous()
         assert cos.shape == sin.shape and cos.shape[0] == T
         p.rot_pairs, p.cos, p.sin = cos.shape[1], cos.data_ptr(), sin.data_ptr()
-    _fill_out(p, out, T, H, heads_per_block)
+    keep = _fill_out(p, out, T, H, heads_per_block, block_out)
     check(lib.magi_qk_norm_rope_fwd(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
     return out
 
 
-def head_block_copy(x: torch.Tensor, out: torch.Tensor, heads_per_block: int = 0, stream=None) -> torch.Tensor:
+def head_block_copy(x: torch.Tensor, out: Optional[torch.Tensor], heads_per_block: int = 0, stream=None, block_out=None
+                    ) -> Optional[torch.Tensor]:
     """Strided bf16 copy -> out with the same destination addressing as qk_norm_rope.
 
     x is [T,H,128], or a source-blocked [B, T, H/B, 128] ("(cp sq) hn hd", what the output all-to-all delivers),
@@ -128,12 +132,20 @@ def head_block_copy(x: torch.Tensor, out: torch.Tensor, heads_per_block: int = 0
         p.x_heads_per_block, p.T, p.H = hb, T, H
     else:
         p.x, p.x_stride_t, p.x_stride_h, p.T, p.H = x.data_ptr(), x.stride(0), x.stride(1), T, H
-    _fill_out(p, out, T, H, heads_per_block)
+    keep = _fill_out(p, out, T, H, heads_per_block, block_out)
     check(lib.magi_head_block_copy(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
     return out
 
 
-def _fill_out(p, out, T, H, heads_per_block):
+def _fill_out(p, out, T, H, heads_per_block, block_out=None):
+    if block_out is not None:
+        ptrs, stride_t, stride_h = block_out
+        if not heads_per_block or H % heads_per_block or len(ptrs) != H // heads_per_block:
+            raise ValueError("block_out needs heads_per_block dividing H and one pointer per block")
+        arr = (C.c_void_p * len(ptrs))(*[int(a) for a in ptrs])
+        p.out_block_ptrs = C.cast(arr, C.POINTER(C.c_void_p))
+        p.out_stride_t, p.out_stride_h, p.heads_per_block = int(stride_t), int(stride_h), heads_per_block
+        return arr  # the caller keeps it alive until the call returns
     if out.dtype != torch.bfloat16 or not out.is_cuda or out.stride(-1) != 1:
         raise ValueError("out must be a CUDA bf16 tensor with a contiguous last dim")
     if heads_per_block and heads_per_block < H:
@@ -208,7 +220,7 @@ def chunk_attn(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
                prefix_chunk_ids: Sequence[int] = (), out: Optional[torch.Tensor] = None, return_lse: bool = True,
                impl: str = "tcgen05", stream=None, q_scale: Optional[torch.Tensor] = None,
                k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None,
-               scale_chunk_tokens: int = 0, q_lo: Optional[torch.Tensor] = None
+               scale_chunk_tokens: int = 0, q_lo: Optional[torch.Tensor] = None, o_peers=None
                ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """General entry: several k intervals per q-range (k_range_offsets) and a paged prefix.
 
@@ -243,9 +255,21 @@ def chunk_attn(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
         if cache is None:
             raise ValueError("no keys: k is empty and there is no cache")
         p.total_k, p.n_kv_heads = 0, cache.n_kv_heads
-    if out is None:
-        out = torch.empty(Tq, Hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
-    p.out, p.o_stride_t, p.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+    keep_peers = None
+    if o_peers is not None:
+        # fused output exchange: (ptrs per rank, token offsets [cp+1], first global head of this rank, stride_t, stride_h)
+        ptrs, offs, head_off, st_t, st_h = o_peers
+        a_ptrs = (C.c_void_p * len(ptrs))(*[int(a) for a in ptrs])
+        a_offs = (C.c_int32 * len(offs))(*[int(o) for o in offs])
+        keep_peers = (a_ptrs, a_offs)
+        p.o_peer_ptrs = C.cast(a_ptrs, C.POINTER(C.c_void_p))
+        p.o_peer_offsets = C.cast(a_offs, C.POINTER(C.c_int32))
+        p.n_o_peers, p.o_head_offset, p.o_stride_t, p.o_stride_h = len(ptrs), int(head_off), int(st_t), int(st_h)
+        return_lse = False
+    else:
+        if out is None:
+            out = torch.empty(Tq, Hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        p.out, p.o_stride_t, p.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
     lse = torch.empty(Tq, Hq, dtype=torch.float32, device=dev) if return_lse else None
     p.lse = lse.data_ptr() if lse is not None else None
     p.total_q, p.n_q_heads = Tq, Hq
@@ -287,6 +311,42 @@ def quantize_e4m3(x: torch.Tensor, chunk_tokens: int, stream=None, residual: boo
                                           x8.data_ptr(), lo.data_ptr() if residual else None, scales.data_ptr(),
                                           _stream(stream)), ctx.handle)
     return (x8, scales, lo) if residual else (x8, scales)
+
+
+class PeerBuffer:
+    """A device buffer other ranks of the box can map (CUDA IPC; plain peer loads / stores over NVLink, no multicast)."""
+
+    def __init__(self, nbytes: int, device=None):
+        self.ctx = Context.get(device)
+        ptr = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        check(lib.magi_peer_alloc(self.ctx.handle, int(nbytes), C.byref(ptr), handle), self.ctx.handle)
+        self.ptr, self.handle, self.nbytes = ptr.value, handle.raw, int(nbytes)
+        self._opened = []
+
+    def open_peer(self, handle: bytes) -> int:
+        ptr = C.c_void_p()
+        check(lib.magi_peer_open(self.ctx.handle, handle, C.byref(ptr)), self.ctx.handle)
+        self._opened.append(ptr.value)
+        return ptr.value
+
+    def as_tensor(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        """View of the local buffer as a torch tensor (no copy; the PeerBuffer must outlive the tensor)."""
+        n = int(np.prod(shape))
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        assert n * itemsize <= self.nbytes
+        iface = {"shape": (n,), "typestr": {2: "<i2", 4: "<i4", 1: "|u1"}[itemsize], "data": (self.ptr, False), "version": 3}
+        holder = type("_CudaArray", (), {"__cuda_array_interface__": iface})()
+        t = torch.as_tensor(holder, device=torch.device("cuda", self.ctx.device))
+        return t.view(dtype).view(*shape)
+
+    def close(self):
+        for ptr in self._opened:
+            lib.magi_peer_close(self.ctx.handle, ptr)
+        self._opened = []
+        if self.ptr:
+            lib.magi_peer_free(self.ctx.handle, self.ptr)
+            self.ptr = None
 
 
 def flex_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_ranges: torch.Tensor, k_ranges: torch.Tensor,

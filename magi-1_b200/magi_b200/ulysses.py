@@ -166,3 +166,100 @@ class UlyssesAttention:
             dst = out.view(s_loc, cp, self.hkv_loc, g, HEAD_DIM)[:, :, :, i * gsub:(i + 1) * gsub]
             src = o_recv.view(cp, s_loc, self.hkv_loc, gsub, HEAD_DIM).permute(1, 0, 2, 3, 4)
             dst.copy_(src)
+
+
+class FusedUlyssesAttention:
+    """Ulysses attention with both exchanges fused into their producer kernels over NVLink peer memory.
+
+    Same contract as UlyssesAttention.forward (bf16), but no all-to-all is launched:
+      * the prologue kernels store each rank's share of the heads straight into that rank's receive buffers
+        (the "scatter heads" exchange, context_parallel.py:381-401, becomes the prologue's store address);
+      * the attention kernel's epilogue stores every output row straight into the owning rank's result buffer at this
+        rank's global head position (the "gather heads" exchange and the final "(cp sq) hn hd -> sq (cp hn) hd"
+        re-layout, context_parallel.py:404-423 and :596, become the epilogue's store address).
+    Buffers are cudaMalloc'ed by the library and mapped by the other ranks through CUDA IPC: plain peer stores, no
+    multicast object, TMA only ever reads local memory.  Two tiny NCCL all-reduces per call act as stream-ordered
+    barriers ("all receive buffers are complete", "all results are complete"); successive calls need nothing more, as
+    a rank can only reach the next call's stores after every rank has passed the previous barrier.
+    The returned tensor is a view of this object's result buffer and is overwritten by the next call.
+    """
+
+    def __init__(self, cp_group, n_q_heads: int, n_kv_heads: int, split_sizes: Sequence[int]):
+        from . import ops
+        self.ops = ops
+        self.group = cp_group
+        self.cp = dist.get_world_size(cp_group)
+        self.rank = dist.get_rank(cp_group)
+        cp = self.cp
+        if n_q_heads % cp or n_kv_heads % cp:
+            raise ValueError(f"{n_q_heads}/{n_kv_heads} heads cannot be split over {cp} ranks (KV-head replication is only "
+                             f"implemented in UlyssesAttention)")
+        if cp > 16:
+            raise ValueError("at most 16 ranks")
+        self.hq, self.hkv = n_q_heads, n_kv_heads
+        self.hq_loc, self.hkv_loc = n_q_heads // cp, n_kv_heads // cp
+        self.splits = [int(s) for s in split_sizes]
+        if len(self.splits) != cp:
+            raise ValueError("split_sizes must have one entry per rank")
+        self.offsets = [0]
+        for s in self.splits:
+            self.offsets.append(self.offsets[-1] + s)
+        S, s_max = self.offsets[-1], max(self.splits)
+        self.S, self.s_loc = S, self.splits[self.rank]
+        dev = torch.cuda.current_device()
+        self.buf_q = ops.PeerBuffer(S * self.hq_loc * HEAD_DIM * 2, dev)
+        self.buf_kv = ops.PeerBuffer(S * self.hkv_loc * 2 * HEAD_DIM * 2, dev)
+        self.buf_o = ops.PeerBuffer(s_max * self.hq * HEAD_DIM * 2, dev)
+        handles = [None] * cp
+        dist.all_gather_object(handles, (self.buf_q.handle, self.buf_kv.handle, self.buf_o.handle), group=cp_group)
+        self.peer_q, self.peer_kv, self.peer_o = [], [], []
+        for r in range(cp):
+            if r == self.rank:
+                self.peer_q.append(self.buf_q.ptr), self.peer_kv.append(self.buf_kv.ptr), self.peer_o.append(self.buf_o.ptr)
+            else:
+                hq_, hkv_, ho_ = handles[r]
+                self.peer_q.append(self.buf_q.open_peer(hq_))
+                self.peer_kv.append(self.buf_kv.open_peer(hkv_))
+                self.peer_o.append(self.buf_o.open_peer(ho_))
+        self._flag = torch.zeros(1, dtype=torch.float32, device=torch.device("cuda", dev))
+        self.q_recv = self.buf_q.as_tensor((S, self.hq_loc, HEAD_DIM))
+        self.kv_recv = self.buf_kv.as_tensor((S, self.hkv_loc, 2 * HEAD_DIM))
+        self.out = self.buf_o.as_tensor((s_max, self.hq, HEAD_DIM))
+        self._barrier()
+
+    def _barrier(self):
+        dist.all_reduce(self._flag, group=self.group)
+
+    def forward(self, xq, xk, xv, gq, bq, gk, bk, cos, sin, q_ranges, k_ranges, max_seqlen_q, max_seqlen_k,
+                eps: float = 1e-6, norm_mode: str = "layernorm_1p", cache=None, layer: int = 0,
+                prefix_chunk_ids: Sequence[int] = (), k_range_offsets=None, attn_events: Optional[list] = None):
+        ops = self.ops
+        off = self.offsets[self.rank]
+        kv_row = self.hkv_loc * 2 * HEAD_DIM   # elements per token in a kv receive buffer
+        q_row = self.hq_loc * HEAD_DIM
+        k_dst = [p + off * kv_row * 2 for p in self.peer_kv]
+        v_dst = [p + (off * kv_row + HEAD_DIM) * 2 for p in self.peer_kv]
+        q_dst = [p + off * q_row * 2 for p in self.peer_q]
+        ops.qk_norm_rope(xk, gk, bk, cos, sin, eps, norm_mode, heads_per_block=self.hkv_loc, block_out=(k_dst, kv_row, 2 * HEAD_DIM))
+        ops.head_block_copy(xv, None, heads_per_block=self.hkv_loc, block_out=(v_dst, kv_row, 2 * HEAD_DIM))
+        ops.qk_norm_rope(xq, gq, bq, cos, sin, eps, norm_mode, heads_per_block=self.hq_loc, block_out=(q_dst, q_row, HEAD_DIM))
+        self._barrier()  # every rank's rows have landed in every receive buffer
+        if attn_events is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        ops.chunk_attn(self.q_recv, self.kv_recv[..., :HEAD_DIM], self.kv_recv[..., HEAD_DIM:], q_ranges, k_ranges, max_seqlen_q,
+                       max_seqlen_k, return_lse=False, k_range_offsets=k_range_offsets, cache=cache, layer=layer,
+                       prefix_chunk_ids=prefix_chunk_ids,
+                       o_peers=(self.peer_o, self.offsets, self.rank * self.hq_loc, self.hq * HEAD_DIM, HEAD_DIM))
+        if attn_events is not None:
+            e1.record()
+            attn_events.append((e0, e1))
+        self._barrier()  # every rank's output rows have landed in every result buffer
+        return self.out[:self.s_loc]
+
+    def close(self):
+        torch.cuda.synchronize()
+        self._barrier()
+        torch.cuda.synchronize()
+        for b in (self.buf_q, self.buf_kv, self.buf_o):
+            b.close()

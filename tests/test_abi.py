@@ -45,9 +45,10 @@ def test_struct_layouts_match_the_header(tmp_path):
     probe = tmp_path / "probe.c"
     fields = {
         "magi_attn_params": ["q", "k", "v", "out", "lse", "total_q", "q_ranges", "n_ranges", "softmax_scale", "cache",
-                             "prefix_chunk_ids", "q_scale", "scale_chunk_tokens", "q_lo"],
+                             "prefix_chunk_ids", "q_scale", "scale_chunk_tokens", "q_lo", "o_peer_ptrs", "o_peer_offsets",
+                             "n_o_peers", "o_head_offset"],
         "magi_prologue_params": ["x", "T", "gamma", "eps", "cos", "out", "out_stride_block", "heads_per_block",
-                                 "x_heads_per_block", "x_stride_block"],
+                                 "out_block_ptrs", "x_heads_per_block", "x_stride_block"],
         "magi_kv_cache_desc": ["dtype", "chunk_tokens", "n_kv_heads"],
     }
     body = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]

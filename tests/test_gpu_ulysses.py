@@ -18,7 +18,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, overlap, fp8=False):
+def _worker(rank, world, port, overlap, fp8=False, fused=False):
     for p in (ROOT, os.path.join(ROOT, "magi-1_b200"), os.path.join(ROOT, "tests")):
         if p not in sys.path:
             sys.path.insert(0, p)
@@ -28,7 +28,7 @@ def _worker(rank, world, port, overlap, fp8=False):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     import magi_b200 as mb
     from magi_b200 import host
-    from magi_b200.ulysses import UlyssesAttention
+    from magi_b200.ulysses import FusedUlyssesAttention, UlyssesAttention
     from oracle import chunk_attn_oracle as O
     from gpu_util import as_segments, assert_close, oracle_on_rows
 
@@ -44,12 +44,13 @@ def _worker(rank, world, port, overlap, fp8=False):
     off = sum(splits[:rank])
     sl = slice(off, off + splits[rank])
     qr, kr = host.q_ranges_for_chunks(n, C), host.default_k_ranges(n, C)
-    ua = UlyssesAttention(dist.group.WORLD, Hq, Hkv, splits, overlap_degree=overlap)
+    ua = FusedUlyssesAttention(dist.group.WORLD, Hq, Hkv, splits) if fused else \
+        UlyssesAttention(dist.group.WORLD, Hq, Hkv, splits, overlap_degree=overlap)
     dev = torch.device("cuda", rank)
     for _ in range(2):  # second pass reuses the buffers
         out = ua.forward(xq[sl].to(dev), xk[sl].to(dev), xv[sl].to(dev), gq, bq, gk, bk, cos[sl], sin[sl],
                          torch.as_tensor(qr, device=dev), torch.as_tensor(kr, device=dev), C, S,
-                         fp8_chunk_tokens=C if fp8 else 0)
+                         **({"fp8_chunk_tokens": C} if fp8 else {}))
     torch.cuda.synchronize()
     assert mb.Context.get(rank).status() == 0
     # oracle on the full sequence, restricted to this rank's rows
@@ -61,8 +62,20 @@ def _worker(rank, world, port, overlap, fp8=False):
         assert O.cosine(out.cpu(), ref) >= 0.999, O.cosine(out.cpu(), ref)
     else:
         assert_close(out, ref, what=f"ulysses cp{world} rank {rank}")
+    if fused:
+        out = out.clone()
+        ua.close()
     dist.barrier()
     dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_peer_memory_exchange_matches_oracle(world):
+    """Prologue and attention epilogue store straight into the peers' buffers (CUDA IPC, no all-to-all)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(world, _free_port(), 1, False, True), nprocs=world, join=True)
 
 
 @pytest.mark.parametrize("world,overlap", [(2, 1), (2, 2), (4, 1)])
