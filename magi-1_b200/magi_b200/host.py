@@ -103,3 +103,32 @@ def synthetic_norm_params(seed: int, d: int = HEAD_DIM):
     gamma = 0.1 N(0,1) (applied as gamma + 1), beta = 0.02 N(0,1)."""
     g = torch.Generator(device="cpu").manual_seed(seed + 1000)
     return tuple(s * torch.randn(d, generator=g) for s in (0.1, 0.02, 0.1, 0.02))
+
+
+def cross_attn_ranges(chunk_tokens: int, n_chunks: int, caption_lens: Sequence[int]):
+    """q/kv ranges of the caption cross-attention (PackedCrossAttnParams, inference/model/dit/dit_model.py:220-244):
+    query chunk i (consecutive blocks of chunk_tokens rows) attends to caption i's valid tokens in the packed
+    y_xattn_flat.  Returns (q_ranges [n,2], kv_ranges [n,2]) as int32 arrays."""
+    assert len(caption_lens) == n_chunks
+    cq = np.arange(n_chunks + 1, dtype=np.int64) * chunk_tokens
+    ck = np.concatenate([[0], np.cumsum(np.asarray(caption_lens, dtype=np.int64))])
+    return (np.stack([cq[:-1], cq[1:]], 1).astype(np.int32), np.stack([ck[:-1], ck[1:]], 1).astype(np.int32))
+
+
+def cp_cross_attn_ranges(q_ranges: np.ndarray, kv_ranges: np.ndarray, cp_split_sizes: Sequence[int], cp_rank: int):
+    """Cross-attention ranges of one context-parallel rank: its contiguous slice of the query sequence is intersected
+    with every q segment, the surviving pieces are rebased to the rank's local rows and keep their caption's kv range.
+    Mirrors cp_update_cross_attn_qkv_range (inference/infra/parallelism/context_parallel.py:134-224) for batch 1,
+    cp_shuffle_num 1.  Returns (q_ranges_local, kv_ranges_local, max_seqlen_q)."""
+    bounds = np.concatenate([[0], np.cumsum(np.asarray(cp_split_sizes, dtype=np.int64))])
+    lo, hi = int(bounds[cp_rank]), int(bounds[cp_rank + 1])
+    q_out, k_out = [], []
+    for (qs, qe), kr in zip(np.asarray(q_ranges).reshape(-1, 2), np.asarray(kv_ranges).reshape(-1, 2)):
+        s, e = max(lo, int(qs)), min(hi, int(qe))
+        if s < e:
+            q_out.append([s, e])
+            k_out.append([int(kr[0]), int(kr[1])])
+    q_arr = np.asarray(q_out, dtype=np.int64).reshape(-1, 2)
+    if len(q_arr):
+        q_arr = q_arr - q_arr[:, 0].min()
+    return q_arr.astype(np.int32), np.asarray(k_out, dtype=np.int32).reshape(-1, 2), hi - lo

@@ -46,3 +46,14 @@ def test_synthetic_norm_params_match_oracle():
     from magi_b200 import host
     for a, b in zip(host.synthetic_norm_params(3), O.make_norm_params(3)):
         assert torch.equal(a, b)
+
+
+def test_cross_attention_range_helpers():
+    from magi_b200 import host
+    qr, kr = host.cross_attn_ranges(10, 3, [4, 0, 7])
+    assert qr.tolist() == [[0, 10], [10, 20], [20, 30]] and kr.tolist() == [[0, 4], [4, 4], [4, 11]]
+    splits = host.cp_split_sizes(30, 4)          # 8, 8, 7, 7
+    ql, kl, mq = host.cp_cross_attn_ranges(qr, kr, splits, 1)     # rows 8..16: tail of chunk 0, head of chunk 1
+    assert ql.tolist() == [[0, 2], [2, 8]] and kl.tolist() == [[0, 4], [4, 4]] and mq == 8
+    ql, kl, mq = host.cp_cross_attn_ranges(qr, kr, splits, 3)     # rows 23..30: inside chunk 2
+    assert ql.tolist() == [[0, 7]] and kl.tolist() == [[4, 11]] and mq == 7
