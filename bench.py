@@ -151,7 +151,9 @@ def run_reference(args, w, rank, world):
     line = {"impl": "reference", "metric": "chunk_causal_attn_useful_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": tot_t / args.steps * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": w["name"], "chunk_tokens": C},
+            "config": {"workload": w["name"], "chunk_tokens": C,
+                       "useful_tflop_per_step": useful_flops(w["hq"], C, w["n_chunks"]) * w.get("batch", 1) / 1e12,
+                       "parallelism": "host cpu", "step": "bounded sample of the attention math (see cpu_baseline.sample)"},
             "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)

@@ -15,7 +15,8 @@ def assert_close(got: torch.Tensor, ref: torch.Tensor, max_abs=MAX_ABS, min_cos=
     assert got.shape == ref.shape, (got.shape, ref.shape)
     assert torch.isfinite(got).all(), f"{what}: non-finite output"
     err = (got - ref).abs().max().item()
-    cos = O.cosine(got, ref)
+    # an all-zero reference (q-ranges without keys) has no direction: the max-abs bound alone decides
+    cos = O.cosine(got, ref) if float(ref.abs().max()) > 0 else 1.0
     assert err <= max_abs and cos >= min_cos, f"{what}: max-abs {err:.4g} (<= {max_abs}), cosine {cos:.6f} (>= {min_cos})"
     return err, cos
 

@@ -1,0 +1,64 @@
+"""Property test: random head geometry, ragged q-ranges with gaps, one or several k intervals per q-range (windows with
+k-start > 0, lengths that are not multiples of 128, Lq != Lk, empty k) against the CPU oracle and the diagnostic twin."""
+import numpy as np
+import pytest
+import torch
+from hypothesis import HealthCheck, given, settings, strategies as st
+
+from oracle import chunk_attn_oracle as O
+from gpu_util import as_segments, assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@st.composite
+def problems(draw):
+    hkv = draw(st.sampled_from([1, 2, 3]))
+    group = draw(st.sampled_from([1, 2, 3, 4, 6]))
+    tk = draw(st.integers(1, 700))
+    n = draw(st.integers(1, 5))
+    q_ranges, segs, pos = [], [], 0
+    for _ in range(n):
+        pos += draw(st.integers(0, 40))                      # gap before the range
+        lq = draw(st.integers(1, 400))
+        q_ranges.append([pos, pos + lq])
+        pos += lq
+        m = draw(st.integers(1, 3))
+        cuts = sorted(draw(st.lists(st.integers(0, tk), min_size=2 * m, max_size=2 * m)))
+        ivals = [[cuts[2 * i], cuts[2 * i + 1]] for i in range(m)]   # disjoint, ordered, possibly empty intervals
+        segs.append(ivals)
+    return hkv, group, tk, pos + draw(st.integers(0, 30)), q_ranges, segs, draw(st.integers(0, 2 ** 31 - 1))
+
+
+@settings(max_examples=30, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.data_too_large])
+@given(problems())
+def test_random_rectangles_match_oracle(prob):
+    import magi_b200 as mb
+    hkv, group, tk, tq, q_ranges, segs, seed = prob
+    hq = hkv * group
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(tq, hq, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(tk, hkv, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(tk, hkv, 128, generator=g).to(torch.bfloat16)
+    kr = np.array([iv for s in segs for iv in s], dtype=np.int32).reshape(-1, 2)
+    offs = np.concatenate([[0], np.cumsum([len(s) for s in segs])]).astype(np.int32)
+    qr = np.array(q_ranges, dtype=np.int32)
+    max_q = int((qr[:, 1] - qr[:, 0]).max())
+    out = torch.full((tq, hq, 128), 5.0, dtype=torch.bfloat16, device="cuda")
+    out, lse = mb.chunk_attn(q.cuda(), k.cuda(), v.cuda(), qr, kr, max_q, tk, k_range_offsets=offs, out=out)
+    twin, _ = mb.chunk_attn(q.cuda(), k.cuda(), v.cuda(), qr, kr, max_q, tk, k_range_offsets=offs, impl="simt")
+    torch.cuda.synchronize()
+    assert mb.Context.get().status() == 0
+    ref, ref_lse = O.range_attention(q.float(), k.float(), v.float(), qr, segs)
+    rows = torch.cat([torch.arange(a, b) for a, b in q_ranges])
+    assert_close(out[rows.cuda()], ref[rows], what="tcgen05 vs oracle")
+    assert_close(twin[rows.cuda()], ref[rows], what="simt vs oracle")
+    covered = torch.zeros(tq, dtype=torch.bool)
+    covered[rows] = True
+    assert (out.cpu()[~covered].float() == 5.0).all()          # rows of no range are never written
+    has_keys = torch.tensor([any(b > a for a, b in s) for s in segs])
+    for (a, b), hk in zip(q_ranges, has_keys):
+        if hk:
+            assert torch.allclose(lse.cpu()[a:b], ref_lse[a:b], atol=3e-3, rtol=1e-3)
+        else:                                                    # a q-range without keys: zeros and lse = -inf
+            assert (out.cpu()[a:b].float() == 0).all() and torch.isinf(lse.cpu()[a:b]).all()

@@ -74,3 +74,47 @@ def test_kv_head_replication_rule():
     assert kv_head_replication(8, 8) == 1 and kv_head_replication(8, 2) == 1 and kv_head_replication(2, 4) == 2
     with pytest.raises(ValueError):
         kv_head_replication(8, 3)
+
+
+def _dropout_worker(rank, world, port, flag_dir):
+    """Rank 1 leaves between two exchanges; rank 0 learns of it when its next collective times out (host-side
+    failure detection: no GPU is involved, nothing hangs for longer than the process-group timeout)."""
+    import datetime
+    import sys
+    for p in (ROOT, os.path.join(ROOT, "magi-1_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    from magi_b200.ulysses import UlyssesExchange
+    ex = UlyssesExchange(dist.group.WORLD, [3, 3])
+    send = torch.arange(2 * 3 * 2 * 4, dtype=torch.float32).view(2, 3, 2, 4) + 100 * rank
+    recv, w = ex.scatter_heads(send)
+    w.wait()                                        # first exchange: both ranks take part
+    assert recv.shape == (6, 2, 4)
+    if rank == 1:
+        open(os.path.join(flag_dir, "rank1_left"), "w").close()
+        os._exit(0)                                 # leaves between steps, nothing of its own in flight
+    failed = False
+    try:
+        _, w = ex.scatter_heads(send)
+        w.wait()
+    except Exception:
+        failed = True
+    assert failed, "the exchange with a missing rank must fail with an error, not return"
+    open(os.path.join(flag_dir, "rank0_detected"), "w").close()
+    os._exit(0)
+
+
+def test_missing_rank_is_detected_by_timeout(tmp_path):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_dropout_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    assert (tmp_path / "rank1_left").exists() and (tmp_path / "rank0_detected").exists()
