@@ -1,6 +1,7 @@
 """Benchmark of the chunk-causal attention hot path (prologue -> [Ulysses in] -> attention -> [Ulysses out]).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3|cfg1] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3|cfg1|cfg2|cfg4] [--exchange fused|nccl]
+                    [--impl ours|reference] [--no-e2e] [--no-cpu-baseline]
 
 One process per GPU (under torchrun for N > 1; RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the environment).
 Rank 0 prints ONE JSON line.  A "step" is one pass of the hot path over one batch of seeded synthetic inputs of
