@@ -28,8 +28,8 @@ WORKLOADS = {
     # 24B-style 720p layer: 48/8 heads, 45x80 patches x 6 frames per chunk, 4 chunks, block-causal (cfg 3)
     "cfg3": dict(name="24B-720p: Hq48/Hkv8 d128, 4 chunks x 21600 tok (T24 H45 W80), block-causal, bf16",
                  hq=48, hkv=8, H=45, W=80, frames_per_chunk=6, n_chunks=4, seed=3,
-                 # dram__bytes_read+write of attn_fwd_kernel per launch: ncu capture at cfg1 (589.2 MB, see
-                 # profiles/attn_fwd_kernel_cfg1.md) scaled by the bytes the launch processes (x 2477.3 / 613.4)
+                 # dram__bytes_read+write of attn_fwd_kernel per launch: ncu capture of the cfg1 launch (589.2 MB)
+                 # scaled by the bytes the launch processes (x 2477.3 / 613.4)
                  traffic_bytes=2379.6e6),
     # 4.5B-style layer: 24/8 heads, 30x52 patches x 6 frames per chunk, 4 chunks (cfg 1)
     "cfg1": dict(name="4.5B-style: Hq24/Hkv8 d128, 4 chunks x 9360 tok (T24 H30 W52), block-causal, bf16",
