@@ -1,0 +1,131 @@
+"""Host-side mirror of the reference's attention module surface for the single-GPU strategy
+(FullyParallelAttention with cp_strategy == "none", inference/model/dit/dit_module.py:1166-1173): the metadata types
+the path consumes (inference/common/dataclass.py:22-83), the KV-cache gate and update rule
+(adjust_key_and_value_for_inference / _full_adjust_key_and_value, dit_module.py:891-946) on top of the chunk-paged
+cache, and core_attention (:1023-1066).  Same names, same argument meaning; tensors are never concatenated or copied
+into a flat per-layer buffer - clean chunks live in pages and are read in place.
+"""
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import ops
+
+HEAD_DIM = 128
+
+
+@dataclass(frozen=True)
+class PackedCoreAttnParams:
+    """q_range / k_range int32 [n, 2] on the device plus their numpy mirrors (inference/common/dataclass.py:22-30)."""
+    q_range: torch.Tensor
+    k_range: torch.Tensor
+    np_q_range: np.ndarray
+    np_k_range: np.ndarray
+    max_seqlen_q: int
+    max_seqlen_k: int
+
+    @classmethod
+    def from_numpy(cls, q_range: np.ndarray, k_range: np.ndarray, device) -> "PackedCoreAttnParams":
+        q_range = np.asarray(q_range, dtype=np.int32).reshape(-1, 2)
+        k_range = np.asarray(k_range, dtype=np.int32).reshape(-1, 2)
+        return cls(torch.as_tensor(q_range, device=device), torch.as_tensor(k_range, device=device), q_range, k_range,
+                   int((q_range[:, 1] - q_range[:, 0]).max()), int(k_range.max() - k_range.min()))
+
+
+@dataclass(frozen=True)
+class ModelMetaArgs:
+    """The fields of the reference's ModelMetaArgs (inference/common/dataclass.py:44-59) that this path reads."""
+    slice_point: int
+    denoising_range_num: int
+    clip_token_nums: int
+    core_attn_params: PackedCoreAttnParams
+    extract_prefix_video_feature: bool = False
+    fwd_extra_1st_chunk: bool = False
+    distill_nearly_clean_chunk: bool = False
+    cp_split_sizes: Optional[List[int]] = None
+
+
+class InferenceParams:
+    """max_batch_size / max_sequence_length / update_kv_cache as in the reference (inference/common/dataclass.py:62-83);
+    key_value_memory_dict[layer] of the reference becomes ONE chunk-paged cache shared by all layers (created on first
+    use, pages of clip_token_nums tokens)."""
+
+    def __init__(self, max_batch_size: int, max_sequence_length: int, n_layers: int = 1, kv_dtype: str = "bf16"):
+        if max_batch_size != 1:
+            raise ValueError("the KV cache path runs with max_batch_size == 1 (as every shipped reference config does)")
+        self.max_batch_size = max_batch_size
+        self.max_sequence_length = max_sequence_length
+        self.sequence_len_offset = 0
+        self.update_kv_cache = False
+        self.n_layers = n_layers
+        self.kv_dtype = kv_dtype
+        self.cache: Optional[ops.ChunkPagedKVCache] = None
+
+    def get_cache(self, chunk_tokens: int, n_kv_heads: int, device) -> ops.ChunkPagedKVCache:
+        if self.cache is None:
+            max_chunks = max(1, self.max_sequence_length // chunk_tokens)
+            self.cache = ops.ChunkPagedKVCache(self.n_layers, max_chunks, chunk_tokens, n_kv_heads, dtype=self.kv_dtype,
+                                               device=device)
+        elif self.cache.chunk_tokens != chunk_tokens or self.cache.n_kv_heads != n_kv_heads:
+            raise ValueError("the cache was created for another chunk size / head count")
+        return self.cache
+
+
+class ChunkCausalSelfAttention:
+    """One layer's self-attention core: prologue -> KV-cache gate -> chunk-causal attention."""
+
+    def __init__(self, layer_number: int, n_q_heads: int, n_kv_heads: int, q_gamma, q_beta, k_gamma, k_beta,
+                 eps: float = 1e-6, norm_mode: str = "layernorm_1p"):
+        self.layer_number, self.hq, self.hkv = layer_number, n_q_heads, n_kv_heads
+        self.q_gamma, self.q_beta, self.k_gamma, self.k_beta = q_gamma, q_beta, k_gamma, k_beta
+        self.eps, self.norm_mode = eps, norm_mode
+
+    # get_q / get_k (dit_module.py:953-980) after the projection: x [(sq b), heads, 128] bf16 views
+    def get_q(self, xq, cos_emb, sin_emb):
+        return ops.qk_norm_rope(xq, self.q_gamma, self.q_beta, cos_emb, sin_emb, self.eps, self.norm_mode)
+
+    def get_k(self, xk, cos_emb, sin_emb):
+        return ops.qk_norm_rope(xk, self.k_gamma, self.k_beta, cos_emb, sin_emb, self.eps, self.norm_mode)
+
+    def adjust_key_and_value_for_inference(self, key: torch.Tensor, value: torch.Tensor,
+                                           inference_params: Optional[InferenceParams], meta_args: ModelMetaArgs
+                                           ) -> Tuple[Optional[ops.ChunkPagedKVCache], Sequence[int]]:
+        """The reference's gate and update rule (dit_module.py:891-946), on pages.
+
+        Touches the cache only if extract_prefix_video_feature or fwd_extra_1st_chunk or slice_point > 0.  Then the
+        prefix is chunks 0 .. slice_point-1 (read in place by the kernel), and with update_kv_cache the current chunks
+        are written to pages slice_point + j - all of them, or all but the last when distill_nearly_clean_chunk.
+        Returns (cache or None, prefix chunk ids); key / value themselves are used as they are."""
+        if inference_params is None:
+            return None, ()
+        if not (meta_args.extract_prefix_video_feature or meta_args.fwd_extra_1st_chunk or meta_args.slice_point > 0):
+            return None, ()
+        C = meta_args.clip_token_nums
+        cache = inference_params.get_cache(C, self.hkv, key.device)
+        if inference_params.update_kv_cache:
+            n_tok = key.shape[0] - C if meta_args.distill_nearly_clean_chunk else key.shape[0]
+            if (meta_args.slice_point * C + n_tok) > inference_params.max_sequence_length:
+                raise ValueError("KV cache update beyond max_sequence_length")
+            for j in range((n_tok + C - 1) // C):
+                lo, hi = j * C, min((j + 1) * C, n_tok)
+                cache.append(self.layer_number, meta_args.slice_point + j, key[lo:hi], value[lo:hi])
+        return cache, list(range(meta_args.slice_point))
+
+    def core_attention(self, query, key, value, meta_args: ModelMetaArgs, cache=None, prefix_chunk_ids=()):
+        p = meta_args.core_attn_params
+        out, _ = ops.chunk_attn(query, key, value, p.q_range, p.k_range, p.max_seqlen_q, p.max_seqlen_k, cache=cache,
+                                layer=self.layer_number, prefix_chunk_ids=prefix_chunk_ids, return_lse=False)
+        return out
+
+    def forward(self, xq, xk, xv, inference_params: Optional[InferenceParams], rotary_pos_emb: torch.Tensor,
+                meta_args: ModelMetaArgs) -> torch.Tensor:
+        """xq [(sq b), Hq, 128], xk / xv [(sq b), Hkv, 128]: the q / k / v projections (bf16, any strides);
+        rotary_pos_emb [(sq), 96] = cat(sin, cos) as LearnableRotaryEmbeddingCat returns it.  Returns
+        core_attn_out [(sq b), Hq, 128]."""
+        sin_emb, cos_emb = rotary_pos_emb.tensor_split(2, -1)
+        key = self.get_k(xk, cos_emb, sin_emb)
+        query = self.get_q(xq, cos_emb, sin_emb)
+        cache, prefix = self.adjust_key_and_value_for_inference(key, xv, inference_params, meta_args)
+        return self.core_attention(query, key, xv, meta_args, cache, prefix)

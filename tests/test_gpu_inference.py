@@ -1,0 +1,81 @@
+"""The reference's denoising schedule driven through the layer mirror (prologue -> KV-cache gate/update -> attention)
+against the oracle's flat-buffer restatement of _full_adjust_key_and_value + the per-range attention loop.
+Steps follow the shipped 24B schedule (4 chunks, window 4): plain steps, the clean re-forward of a finished chunk
+(fwd_extra_1st_chunk), steps that read a growing cached prefix with windowed k-ranges, and a distilled step that must
+not store its last chunk."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import chunk_attn_oracle as O
+from gpu_util import as_segments, assert_close
+
+pytestmark = pytest.mark.gpu
+
+C, HQ, HKV = 260, 6, 2     # 260 tokens per chunk = 2 frames of 10 x 13 patches
+
+
+def _step(layer, ip, ref_cache, gen, params, sin_cos_full, slice_point, n, k_chunks, update, extra=False, distill=False):
+    import magi_b200 as mb
+    from magi_b200.inference import ModelMetaArgs, PackedCoreAttnParams
+    gq, bq, gk, bk = params
+    T = n * C
+    xq = torch.randn(T, HQ, 128, generator=gen).to(torch.bfloat16)
+    xk = torch.randn(T, HKV, 128, generator=gen).to(torch.bfloat16)
+    xv = torch.randn(T, HKV, 128, generator=gen).to(torch.bfloat16)
+    # rotary rows of the frames being forwarded: absolute positions slice_point .. slice_point + n
+    sin, cos = sin_cos_full
+    rows = slice(slice_point * C, (slice_point + n) * C)
+    rope = torch.cat([sin[rows], cos[rows]], dim=-1)
+    qr = O.consecutive_q_ranges(n, C)
+    kr = np.array([[a * C, b * C] for a, b in k_chunks], dtype=np.int32)
+    meta = ModelMetaArgs(slice_point=slice_point, denoising_range_num=n, clip_token_nums=C,
+                         core_attn_params=PackedCoreAttnParams.from_numpy(qr, kr, "cuda"),
+                         fwd_extra_1st_chunk=extra, distill_nearly_clean_chunk=distill)
+    ip.update_kv_cache = update
+    out = layer.forward(xq.cuda(), xk.cuda(), xv.cuda(), ip, rope.cuda(), meta)
+    torch.cuda.synchronize()
+    assert mb.Context.get().status() == 0
+    # oracle: same prologue, flat cache, cat(prefix, current), per-range attention
+    q_ref = O.qk_prologue(xq, gq, bq, cos[rows], sin[rows]).float()
+    k_ref = O.qk_prologue(xk, gk, bk, cos[rows], sin[rows]).float()
+    kv = torch.cat([k_ref, xv.float()], dim=-1)
+    k_all, v_all = ref_cache.adjust(kv, slice_point, C, update, fwd_extra_1st_chunk=extra, distill_nearly_clean_chunk=distill)
+    ref, _ = O.range_attention(q_ref, k_all, v_all, qr, as_segments(kr))
+    assert_close(out, ref, what=f"slice_point {slice_point}, n {n}, k {k_chunks}")
+
+
+def test_denoising_schedule_with_paged_cache_matches_flat_cache_oracle():
+    from magi_b200 import host
+    from magi_b200.inference import ChunkCausalSelfAttention, InferenceParams
+    params = host.synthetic_norm_params(61)
+    layer = ChunkCausalSelfAttention(1, HQ, HKV, *params)
+    ip = InferenceParams(max_batch_size=1, max_sequence_length=5 * C, n_layers=2)
+    ref_cache = O.RefKVCache(5 * C, HKV)
+    gen = torch.Generator().manual_seed(61)
+    sin_cos = O.rope_table(10, 10, 13)          # 5 chunks x 2 frames
+    run = lambda *a, **k: _step(layer, ip, ref_cache, gen, params, sin_cos, *a, **k)
+    # stages 0..3: the window fills up; nothing is cached yet (the gate stays closed even with update_kv_cache set)
+    run(0, 1, [(0, 1)], update=True)
+    run(0, 3, [(0, 1), (0, 2), (0, 3)], update=False)
+    assert ip.cache is None
+    run(0, 4, [(0, 1), (0, 2), (0, 3), (0, 4)], update=True)
+    assert ip.cache is None
+    # stage 4, first step: chunk 0 is re-forwarded clean together with chunks 1..3 and everything is stored
+    run(0, 4, [(0, 1), (0, 2), (0, 3), (0, 4)], update=True, extra=True)
+    # stage 4, later steps: chunk 0 comes from the cache; the CFG pass without update leaves the cache alone
+    run(1, 3, [(0, 2), (0, 3), (0, 4)], update=True)
+    run(1, 3, [(0, 2), (0, 3), (0, 4)], update=False)
+    # stage 5, first step: the clean chunk 1 sees only itself, windows start at chunk 1 (k-start > 0)
+    run(1, 3, [(1, 2), (1, 3), (1, 4)], update=True, extra=True)
+    run(2, 2, [(1, 3), (1, 4)], update=True)
+    # a distilled step: the last (nearly clean) chunk must not be stored
+    run(2, 3, [(1, 3), (1, 4), (2, 5)], update=True, distill=True)
+    run(3, 2, [(2, 4), (2, 5)], update=True)
+    # the cached pages hold exactly what the flat buffer holds
+    for cid in range(4):
+        k_page, v_page = ip.cache.read(1, cid)
+        flat = ref_cache.buf[cid * C:(cid + 1) * C]
+        assert (k_page.cpu().float() - flat[..., :128]).abs().max().item() <= 2 ** -5
+        assert torch.equal(v_page.cpu().float(), flat[..., 128:])
+    ip.cache.close()
