@@ -102,7 +102,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(&s_full[x], 1);
-      mbar_init(&p_full[x], 128);
+      mbar_init(&p_full[x], 4);  // one arrival per softmax warp: arrivals on one mbarrier serialise
       mbar_init(&o_full[x], 1);
     }
     *abort_flag = 0;
@@ -305,7 +305,8 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         m_used = m_cur;
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&p_full[x]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[x]);
       }
     }
     if (ok) ok = mbar_wait(&o_full[x], (n_tiles - 1) & 1, abort_flag);

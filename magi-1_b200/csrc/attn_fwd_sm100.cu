@@ -143,7 +143,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(&s_full[x], 1);
-      mbar_init(&p_full[x], 128);
+      mbar_init(&p_full[x], 4);  // one arrival per softmax warp: arrivals on one mbarrier serialise
       mbar_init(&o_full[x], 1);
     }
     *abort_flag = 0;
@@ -393,7 +393,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 5);
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&p_full[x]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[x]);
         if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 6);
       }
     }

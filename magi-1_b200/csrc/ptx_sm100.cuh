@@ -25,32 +25,34 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// try_wait with a suspend-time hint: the hardware parks the thread until the phase completes or the hint (in
+// nanoseconds) runs out, so a waiting warp does not compete for issue slots with the warps doing the work.
+#ifndef MAGI_WAIT_HINT_NS
+#define MAGI_WAIT_HINT_NS 200000
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)MAGI_WAIT_HINT_NS)
       : "memory");
   return ok != 0;
 }
 
-// Bounded wait: spins on try_wait, gives up after `limit_cycles` of clock64 or as soon as *abort_flag
-// is non-zero (another role of this CTA already gave up).  Returns false on give-up.
+// Bounded wait: repeats try_wait, gives up after `limit_cycles` of clock64 or as soon as *abort_flag is non-zero
+// (another role of this CTA already gave up).  Returns false on give-up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           long long limit_cycles = 1000000000LL) {
   if (mbar_try_wait(bar, parity)) return true;
-  long long t0 = clock64();
-  uint32_t spins = 0;
+  const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0xff) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > limit_cycles) {
-        *abort_flag = 1;
-        return false;
-      }
+    if (*abort_flag) return false;
+    if (clock64() - t0 > limit_cycles) {
+      *abort_flag = 1;
+      return false;
     }
   }
   return true;
