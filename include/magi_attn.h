@@ -198,6 +198,14 @@ typedef struct {
   const int32_t* o_peer_offsets;   /* [n_o_peers + 1] */
   int32_t n_o_peers;
   int32_t o_head_offset;
+  /* Optional head-block output layout: with o_heads_per_block > 0 the 128 columns of (global) head h start at
+   * (h / o_heads_per_block) * o_stride_block + (h % o_heads_per_block) * o_stride_h instead of h * o_stride_h.  This
+   * writes core_attn_out (and, with `out` advanced by one block width, cross_attn_out) straight into the operand of the
+   * output projection, i.e. the concat + rearrange "sq b (n hn hd) -> sq b (hn n hd)", n=2, hn=8 of attn_linear_proj
+   * (inference/model/dit/dit_module.py:1332-1346): o_heads_per_block = Hq/8, o_stride_block = 2 * (Hq/8) * 128. */
+  int32_t o_heads_per_block;
+  int32_t reserved2;
+  int64_t o_stride_block;
 } magi_attn_params;
 MAGI_API int magi_chunk_attn_fwd(magi_ctx* ctx, const magi_attn_params* p, void* stream);
 /* Diagnostic twin: same plan, same arguments (bf16 only), plain CUDA-core arithmetic in fp32.  It exists so a

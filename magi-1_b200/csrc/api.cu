@@ -334,6 +334,8 @@ static int attn_common(magi_ctx* ctx, const magi_attn_params* p, void* stream, i
   if (p->n_q_heads > 65535) return set_err(ctx, MAGI_E_BADARG, "attn: too many heads");
   if ((reinterpret_cast<uintptr_t>(p->out) & 15) || (p->o_stride_t & 7) || (p->o_stride_h & 7))
     return set_err(ctx, MAGI_E_ALIGN, "attn: out must be 16-byte aligned with strides multiple of 8 elements");
+  if (p->o_heads_per_block < 0 || (p->o_heads_per_block > 0 && (p->o_stride_block & 7)))
+    return set_err(ctx, MAGI_E_ALIGN, "attn: o_heads_per_block must be >= 0 and o_stride_block a multiple of 8 elements");
   if (p->n_o_peers != 0) {
     if (p->n_o_peers < 0 || p->n_o_peers > 16 || !p->o_peer_ptrs || !p->o_peer_offsets || impl == 2 || p->lse)
       return set_err(ctx, MAGI_E_BADARG, "attn: fused output exchange needs 1..16 peers, pointer and offset tables, no lse, tensor-core kernel");

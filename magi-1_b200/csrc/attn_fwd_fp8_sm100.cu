@@ -31,6 +31,8 @@ struct Attn8Params {
   const void* plan;
   __nv_bfloat16* out;
   int64_t o_stride_t, o_stride_h;
+  int64_t o_stride_block;  // head-block output layout (o_hpb > 0): see head_col()
+  int o_hpb;
   float* lse;
   int n_q_heads, n_kv_heads, group;
   float scale_log2;
@@ -76,7 +78,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   if (n_tiles == 0) {
     for (int idx = threadIdx.x; idx < it.q_rows * (kHeadDim / 8); idx += blockDim.x) {
       const int r = idx / (kHeadDim / 8), c = idx % (kHeadDim / 8);
-      *reinterpret_cast<uint4*>(p.out + (int64_t)(it.q_row0 + r) * p.o_stride_t + (int64_t)head * p.o_stride_h + c * 8) =
+      *reinterpret_cast<uint4*>(p.out + (int64_t)(it.q_row0 + r) * p.o_stride_t + head_col(p, head) + c * 8) =
           make_uint4(0, 0, 0, 0);
     }
     if (p.lse)
@@ -315,7 +317,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const int r_in_item = x * kTileM + row;
       const bool valid_row = r_in_item < it.q_rows;
       const float inv = 1.0f / l;
-      __nv_bfloat16* dst = p.out + (int64_t)(it.q_row0 + r_in_item) * p.o_stride_t + (int64_t)head * p.o_stride_h;
+      __nv_bfloat16* dst = p.out + (int64_t)(it.q_row0 + r_in_item) * p.o_stride_t + head_col(p, head);
 #pragma unroll 1
       for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t o[32];
@@ -383,6 +385,8 @@ int launch_attn_fp8(magi_ctx* ctx, const magi_attn_params* p, int max_items, cud
   kp.out = reinterpret_cast<__nv_bfloat16*>(p->out);
   kp.o_stride_t = p->o_stride_t;
   kp.o_stride_h = p->o_stride_h;
+  kp.o_stride_block = p->o_stride_block;
+  kp.o_hpb = p->o_heads_per_block;
   kp.lse = p->lse;
   kp.n_q_heads = p->n_q_heads;
   kp.n_kv_heads = p->n_kv_heads;

@@ -31,6 +31,8 @@ struct AttnKernelParams {
   const void* plan;
   __nv_bfloat16* out;
   int64_t o_stride_t, o_stride_h;
+  int64_t o_stride_block;  // head-block output layout (o_hpb > 0): see head_col()
+  int o_hpb;
   float* lse;
   int n_q_heads;
   int group;          // q heads per kv head
@@ -116,7 +118,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (n_tiles == 0) {  // a q-range with no keys: define the output as zeros, lse = -inf
     for (int idx = threadIdx.x; idx < it.q_rows * (kHeadDim / 8); idx += blockDim.x) {
       const int r = idx / (kHeadDim / 8), c = idx % (kHeadDim / 8);
-      *reinterpret_cast<uint4*>(p.out + (int64_t)(it.q_row0 + r) * p.o_stride_t + (int64_t)head * p.o_stride_h + c * 8) =
+      *reinterpret_cast<uint4*>(p.out + (int64_t)(it.q_row0 + r) * p.o_stride_t + head_col(p, head) + c * 8) =
           make_uint4(0, 0, 0, 0);
     }
     if (p.lse)
@@ -437,9 +439,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (p.n_peers > 0) {  // the row goes to the rank that owns this token, at this rank's global head position
             int d = 0;
             while (d + 1 < p.n_peers && t >= p.peer_off[d + 1]) ++d;
-            dst_row = p.peer_out[d] + (int64_t)(t - p.peer_off[d]) * p.o_stride_t + (int64_t)(p.head_offset + head) * p.o_stride_h;
+            dst_row = p.peer_out[d] + (int64_t)(t - p.peer_off[d]) * p.o_stride_t + head_col(p, p.head_offset + head);
           } else {
-            dst_row = p.out + (int64_t)t * p.o_stride_t + (int64_t)head * p.o_stride_h;
+            dst_row = p.out + (int64_t)t * p.o_stride_t + head_col(p, head);
           }
           *reinterpret_cast<uint4*>(dst_row + ((l16 ^ (rr & 15)) << 3)) = v;
         }
@@ -552,6 +554,8 @@ int launch_attn_bf16(magi_ctx* ctx, const magi_attn_params* p, int max_items, cu
   kp.out = reinterpret_cast<__nv_bfloat16*>(p->out);
   kp.o_stride_t = p->o_stride_t;
   kp.o_stride_h = p->o_stride_h;
+  kp.o_stride_block = p->o_stride_block;
+  kp.o_hpb = p->o_heads_per_block;
   kp.lse = p->lse;
   kp.n_q_heads = p->n_q_heads;
   kp.group = p->n_q_heads / p->n_kv_heads;

@@ -17,6 +17,8 @@ struct SimtParams {
   int64_t k_stride_t[2], k_stride_h[2], v_stride_t[2], v_stride_h[2];
   __nv_bfloat16* out;
   int64_t o_stride_t, o_stride_h;
+  int64_t o_stride_block;  // head-block output layout (o_hpb > 0): see head_col()
+  int o_hpb;
   float* lse;
   int n_q_heads, group;
   float scale;
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(256) attn_simt_kernel(SimtParams p) {
     uint2 u;
     u.x = *reinterpret_cast<uint32_t*>(&lo);
     u.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(p.out + row * p.o_stride_t + (int64_t)head * p.o_stride_h + lane * 4) = u;
+    *reinterpret_cast<uint2*>(p.out + row * p.o_stride_t + head_col(p, head) + lane * 4) = u;
     if (p.lse && lane == 0) p.lse[row * p.n_q_heads + head] = l > 0.f ? m + logf(l) : -INFINITY;
   }
 }
@@ -94,6 +96,8 @@ int launch_attn_simt(magi_ctx* ctx, const magi_attn_params* p, int max_items, cu
   sp.out = reinterpret_cast<__nv_bfloat16*>(p->out);
   sp.o_stride_t = p->o_stride_t;
   sp.o_stride_h = p->o_stride_h;
+  sp.o_stride_block = p->o_stride_block;
+  sp.o_hpb = p->o_heads_per_block;
   sp.lse = p->lse;
   sp.n_q_heads = p->n_q_heads;
   sp.group = p->n_q_heads / p->n_kv_heads;

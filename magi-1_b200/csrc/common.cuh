@@ -78,6 +78,14 @@ struct PlanArgs {
 
 void launch_plan(void* workspace, const PlanArgs& a, const PrefixTable& pt, cudaStream_t stream);
 
+// Element offset of head h's 128 output columns inside a token row: h * o_stride_h, or with the head-block layout
+// (o_hpb heads per block, blocks o_stride_block apart) (h / o_hpb) * o_stride_block + (h % o_hpb) * o_stride_h.
+template <class P>
+__device__ __forceinline__ int64_t head_col(const P& p, int h) {
+  return p.o_hpb > 0 ? (int64_t)(h / p.o_hpb) * p.o_stride_block + (int64_t)(h % p.o_hpb) * p.o_stride_h
+                     : (int64_t)h * p.o_stride_h;
+}
+
 }  // namespace magi
 
 // ---- host-side objects -------------------------------------------------------------------------

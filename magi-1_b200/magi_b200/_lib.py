@@ -60,6 +60,7 @@ class AttnParams(C.Structure):
         ("scale_chunk_tokens", C.c_int32), ("reserved", C.c_int32), ("q_lo", C.c_void_p),
         ("o_peer_ptrs", C.POINTER(C.c_void_p)), ("o_peer_offsets", C.POINTER(C.c_int32)),
         ("n_o_peers", C.c_int32), ("o_head_offset", C.c_int32),
+        ("o_heads_per_block", C.c_int32), ("reserved2", C.c_int32), ("o_stride_block", C.c_int64),
     ]
 
 

@@ -73,6 +73,35 @@ class InferenceParams:
         return self.cache
 
 
+class ProjInput:
+    """The operand of the attention output projection, written in place by the two attention calls.
+
+    The reference concatenates core_attn_out and cross_attn_out along the hidden dimension and permutes it with
+    "sq b (n hn hd) -> sq b (hn n hd)", n=2, hn=8 (attn_linear_proj, inference/model/dit/dit_module.py:1332-1346): two
+    extra HBM passes over [sq, 2*Hq*128].  Here `buf` [n_tokens, 2*Hq*128] already has that layout; dest(0) / dest(1)
+    are the keyword arguments that make ops.chunk_attn store core / cross attention heads at their final columns."""
+
+    def __init__(self, n_tokens: int, n_q_heads: int, device, hn: int = 8):
+        if n_q_heads % hn:
+            raise ValueError("the head count must be a multiple of hn")
+        self.n_q_heads, self.hn = n_q_heads, hn
+        self.heads_per_block = n_q_heads // hn
+        self.hd = self.heads_per_block * HEAD_DIM          # width of one (n, hn) piece
+        self.buf = torch.empty(n_tokens, 2 * n_q_heads * HEAD_DIM, dtype=torch.bfloat16, device=device)
+
+    def dest(self, which: int) -> dict:
+        """which = 0: core attention, 1: cross attention."""
+        return dict(out=self.buf[:, which * self.hd:], out_heads_per_block=self.heads_per_block,
+                    out_block_stride=2 * self.hd)
+
+    @staticmethod
+    def reference_layout(core: torch.Tensor, cross: torch.Tensor, hn: int = 8) -> torch.Tensor:
+        """What the reference computes from the two [sq, Hq, 128] outputs (for tests): cat + rearrange."""
+        sq = core.shape[0]
+        x = torch.cat([core.reshape(sq, -1), cross.reshape(sq, -1)], dim=1)           # (n hn hd)
+        return x.view(sq, 2, hn, -1).permute(0, 2, 1, 3).reshape(sq, -1).contiguous()  # (hn n hd)
+
+
 class ChunkCausalSelfAttention:
     """One layer's self-attention core: prologue -> KV-cache gate -> chunk-causal attention."""
 
@@ -113,14 +142,17 @@ class ChunkCausalSelfAttention:
                 cache.append(self.layer_number, meta_args.slice_point + j, key[lo:hi], value[lo:hi])
         return cache, list(range(meta_args.slice_point))
 
-    def core_attention(self, query, key, value, meta_args: ModelMetaArgs, cache=None, prefix_chunk_ids=()):
+    def core_attention(self, query, key, value, meta_args: ModelMetaArgs, cache=None, prefix_chunk_ids=(),
+                       proj_in: Optional[ProjInput] = None):
+        """With proj_in the heads are stored at their final columns of the projection operand (proj_in.buf)."""
         p = meta_args.core_attn_params
+        dest = proj_in.dest(0) if proj_in is not None else {}
         out, _ = ops.chunk_attn(query, key, value, p.q_range, p.k_range, p.max_seqlen_q, p.max_seqlen_k, cache=cache,
-                                layer=self.layer_number, prefix_chunk_ids=prefix_chunk_ids, return_lse=False)
-        return out
+                                layer=self.layer_number, prefix_chunk_ids=prefix_chunk_ids, return_lse=False, **dest)
+        return proj_in.buf if proj_in is not None else out
 
     def forward(self, xq, xk, xv, inference_params: Optional[InferenceParams], rotary_pos_emb: torch.Tensor,
-                meta_args: ModelMetaArgs) -> torch.Tensor:
+                meta_args: ModelMetaArgs, proj_in: Optional[ProjInput] = None) -> torch.Tensor:
         """xq [(sq b), Hq, 128], xk / xv [(sq b), Hkv, 128]: the q / k / v projections (bf16, any strides);
         rotary_pos_emb [(sq), 96] = cat(sin, cos) as LearnableRotaryEmbeddingCat returns it.  Returns
         core_attn_out [(sq b), Hq, 128]."""
@@ -128,4 +160,4 @@ class ChunkCausalSelfAttention:
         key = self.get_k(xk, cos_emb, sin_emb)
         query = self.get_q(xq, cos_emb, sin_emb)
         cache, prefix = self.adjust_key_and_value_for_inference(key, xv, inference_params, meta_args)
-        return self.core_attention(query, key, xv, meta_args, cache, prefix)
+        return self.core_attention(query, key, xv, meta_args, cache, prefix, proj_in)

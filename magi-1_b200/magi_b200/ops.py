@@ -220,11 +220,16 @@ def chunk_attn(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
                prefix_chunk_ids: Sequence[int] = (), out: Optional[torch.Tensor] = None, return_lse: bool = True,
                impl: str = "tcgen05", stream=None, q_scale: Optional[torch.Tensor] = None,
                k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None,
-               scale_chunk_tokens: int = 0, q_lo: Optional[torch.Tensor] = None, o_peers=None
+               scale_chunk_tokens: int = 0, q_lo: Optional[torch.Tensor] = None, o_peers=None,
+               out_heads_per_block: int = 0, out_block_stride: int = 0
                ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """General entry: several k intervals per q-range (k_range_offsets) and a paged prefix.
 
-    bf16 q/k/v, or e4m3 q/k/v (torch.float8_e4m3fn) with the fp32 block scales of quantize_e4m3 (out stays bf16)."""
+    bf16 q/k/v, or e4m3 q/k/v (torch.float8_e4m3fn) with the fp32 block scales of quantize_e4m3 (out stays bf16).
+
+    out_heads_per_block > 0 selects the head-block output layout: `out` is then a 2-D bf16 view [Tq, row_width]
+    (stride(1) == 1) and head h lands at columns (h // hpb) * out_block_stride + (h % hpb) * 128, which is how
+    ProjInput (inference.py) has core and cross attention write the operand of the output projection in place."""
     fp8 = q.dtype == torch.float8_e4m3fn
     in_dtype = torch.float8_e4m3fn if fp8 else torch.bfloat16
     _thd(q, "q", in_dtype)
@@ -267,9 +272,19 @@ def chunk_attn(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
         p.n_o_peers, p.o_head_offset, p.o_stride_t, p.o_stride_h = len(ptrs), int(head_off), int(st_t), int(st_h)
         return_lse = False
     else:
-        if out is None:
-            out = torch.empty(Tq, Hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
-        p.out, p.o_stride_t, p.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+        if out_heads_per_block > 0:
+            if out is None or out.dim() != 2 or out.dtype != torch.bfloat16 or out.stride(1) != 1 or out.shape[0] < Tq:
+                raise ValueError("head-block layout needs out as a 2-D bf16 view [Tq, row_width] with unit column stride")
+            n_blocks = (Hq + out_heads_per_block - 1) // out_heads_per_block
+            if (n_blocks - 1) * out_block_stride + out_heads_per_block * HEAD_DIM > out.shape[1] or \
+                    out_block_stride < out_heads_per_block * HEAD_DIM:
+                raise ValueError("head-block layout does not fit the rows of out")
+            p.out, p.o_stride_t, p.o_stride_h = out.data_ptr(), out.stride(0), HEAD_DIM
+            p.o_heads_per_block, p.o_stride_block = int(out_heads_per_block), int(out_block_stride)
+        else:
+            if out is None:
+                out = torch.empty(Tq, Hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+            p.out, p.o_stride_t, p.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
     lse = torch.empty(Tq, Hq, dtype=torch.float32, device=dev) if return_lse else None
     p.lse = lse.data_ptr() if lse is not None else None
     p.total_q, p.n_q_heads = Tq, Hq
