@@ -1,7 +1,7 @@
 """Benchmark of the chunk-causal attention hot path (prologue -> [Ulysses in] -> attention -> [Ulysses out]).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3|cfg1|cfg2|cfg4] [--exchange fused|nccl]
-                    [--impl ours|reference] [--no-e2e] [--no-cpu-baseline]
+                    [--impl ours|reference] [--no-e2e] [--no-cpu-baseline] [--no-gpu-dispatch-baseline]
 
 One process per GPU (under torchrun for N > 1; RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the environment).
 Rank 0 prints ONE JSON line.  A "step" is one pass of the hot path over one batch of seeded synthetic inputs of
@@ -170,6 +170,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-gpu-dispatch-baseline", action="store_true")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: Ulysses exchange fused into the kernels over peer memory, or NCCL all-to-all + copies")
     args = ap.parse_args()
@@ -412,6 +413,32 @@ def main():
                "h2d_bytes_per_step": h2d * cp, "d2h_bytes_per_step": ho.numel() * 2 * cp,
                "pipeline": "copies overlapped with the neighbouring steps on side streams" if pipelined else "sequential"}
 
+    # ---- secondary baseline, comparison only: the reference's fallback dispatch on this GPU, a loop of flash_attn_func
+    # over the ranges (inference/model/dit/dit_module.py:1049-1065) with the flash-attn build of the image, on the same
+    # prologued Q/K and V.  Never a dispatch target of the library; absent or failing flash-attn leaves the field null.
+    gpu_dispatch = None
+    if cp == 1 and not args.no_gpu_dispatch_baseline and not w.get("fp8") and not w.get("decode"):
+        try:
+            import flash_attn
+            qr_h, kr_h = qr.cpu().numpy(), kr.cpu().numpy()
+
+            def dispatch_loop():
+                return [flash_attn.flash_attn_func(q=q_buf[None, a:b], k=k_buf[None, c:d], v=xv[None, c:d])
+                        for (a, b), (c, d) in zip(qr_h, kr_h)]
+            dispatch_loop()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(3):
+                dispatch_loop()
+            b.record()
+            torch.cuda.synchronize()
+            d_ms = a.elapsed_time(b) / 3
+            gpu_dispatch = {"ms": d_ms, "value": flops / (d_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                            "what": f"loop of flash_attn_func per range, flash-attn {flash_attn.__version__} (reference pins 2.4.2), attention only"}
+        except Exception as e:  # noqa: BLE001 - comparison leg only
+            gpu_dispatch = {"unavailable": str(e)[:160]}
+
     if rank == 0:
         cpu_b = None
         if cp == 1 and not args.no_cpu_baseline:
@@ -454,6 +481,8 @@ def main():
             line["cpu_baseline"] = cpu_b
         if e2e:
             line["e2e"] = e2e
+        if gpu_dispatch:
+            line["gpu_reference_dispatch"] = gpu_dispatch
         print(json.dumps(line), flush=True)
     if cp > 1:
         dist.barrier()

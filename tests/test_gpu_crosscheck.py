@@ -1,0 +1,73 @@
+"""Cross-checks of the kernel and the oracle against two independent implementations on the GPU box:
+
+* torch.nn.functional.scaled_dot_product_attention in fp32 with an explicit boolean block mask, and
+* the third-party kernel the reference itself dispatches to when MagiAttention is absent: a loop of
+  flash_attn_func over the ranges, shaped as in core_attention (inference/model/dit/dit_module.py:1049-1065).
+  The reference pins flash-attn 2.4.2; the image carries a later 2.x, so this check is skipped when that build has no
+  kernel for the device.
+
+Neither is a dispatch target of the library; they are only compared with."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import as_segments, assert_close
+from oracle import chunk_attn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(C, n, Hq, Hkv, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = (torch.randn(n * C, Hq, 128, generator=g)).to(torch.bfloat16)
+    k = (torch.randn(n * C, Hkv, 128, generator=g)).to(torch.bfloat16)
+    v = (torch.randn(n * C, Hkv, 128, generator=g)).to(torch.bfloat16)
+    return q, k, v
+
+
+def test_against_sdpa_with_boolean_block_mask():
+    import magi_b200 as mb
+    from magi_b200 import host
+    C, n, Hq, Hkv = 200, 3, 8, 2
+    q, k, v = _inputs(C, n, Hq, Hkv, 91)
+    qr, kr = host.q_ranges_for_chunks(n, C), host.windowed_k_ranges(0, n, C, [2, 2, 1], 0)   # k-start > 0 for chunk 2
+    out, _ = mb.chunk_attn(q.cuda(), k.cuda(), v.cuda(), qr, kr, C, n * C)
+    mask = O.block_mask(qr, as_segments(kr), n * C, n * C).cuda()
+    qf = q.cuda().float().permute(1, 0, 2)[None]                                    # [1, Hq, S, 128]
+    kf = k.cuda().float().repeat_interleave(Hq // Hkv, dim=1).permute(1, 0, 2)[None]
+    vf = v.cuda().float().repeat_interleave(Hq // Hkv, dim=1).permute(1, 0, 2)[None]
+    with torch.nn.attention.sdpa_kernel(torch.nn.attention.SDPBackend.MATH):
+        ref = torch.nn.functional.scaled_dot_product_attention(qf, kf, vf, attn_mask=mask[None, None])
+    ref = ref[0].permute(1, 0, 2)
+    torch.cuda.synchronize()
+    assert_close(out, ref.cpu(), what="kernel vs SDPA (fp32, boolean block mask)")
+    # and the oracle agrees with SDPA to fp32 rounding
+    want, _ = O.range_attention(q.float(), k.float(), v.float(), qr, as_segments(kr))
+    assert (want - ref.cpu()).abs().max().item() < 2e-5
+
+
+def test_against_the_reference_fallback_loop_of_flash_attn_func():
+    flash_attn = pytest.importorskip("flash_attn")
+    import magi_b200 as mb
+    from magi_b200 import host
+    C, n, Hq, Hkv = 1560, 4, 24, 8                       # one latent frame of 30x52 patches per chunk, 4.5B heads
+    q, k, v = _inputs(C, n, Hq, Hkv, 92)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    qr, kr = host.q_ranges_for_chunks(n, C), host.default_k_ranges(n, C)
+    outs = []
+    try:
+        for i in range(n):                                # dit_module.py:1052-1065 with bs == 1
+            o = flash_attn.flash_attn_func(q=qd[None, qr[i, 0]:qr[i, 1]], k=kd[None, kr[i, 0]:kr[i, 1]],
+                                           v=vd[None, kr[i, 0]:kr[i, 1]], deterministic=False)
+            outs.append(o[0])
+        torch.cuda.synchronize()
+    except RuntimeError as e:                             # e.g. no kernel image for this device in the installed build
+        pytest.skip(f"installed flash-attn {flash_attn.__version__} does not run on this GPU: {str(e)[:120]}")
+    ref = torch.cat(outs, dim=0)
+    out, _ = mb.chunk_attn(qd, kd, vd, qr, kr, C, n * C)
+    torch.cuda.synchronize()
+    # two bf16 kernels with different summation orders: compare both with the fp32 oracle and with each other
+    want, _ = O.range_attention(q.float(), k.float(), v.float(), qr, as_segments(kr))
+    assert_close(out, want, what="kernel vs oracle")
+    assert_close(ref, want, what="flash_attn_func loop vs oracle")
+    assert (out.float() - ref.float()).abs().max().item() <= 2e-2
