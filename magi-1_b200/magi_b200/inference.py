@@ -52,7 +52,8 @@ class InferenceParams:
     key_value_memory_dict[layer] of the reference becomes ONE chunk-paged cache shared by all layers (created on first
     use, pages of clip_token_nums tokens)."""
 
-    def __init__(self, max_batch_size: int, max_sequence_length: int, n_layers: int = 1, kv_dtype: str = "bf16"):
+    def __init__(self, max_batch_size: int, max_sequence_length: int, n_layers: int = 1, kv_dtype: str = "bf16",
+                 max_cached_chunks: Optional[int] = None):
         if max_batch_size != 1:
             raise ValueError("the KV cache path runs with max_batch_size == 1 (as every shipped reference config does)")
         self.max_batch_size = max_batch_size
@@ -61,11 +62,26 @@ class InferenceParams:
         self.update_kv_cache = False
         self.n_layers = n_layers
         self.kv_dtype = kv_dtype
+        self.max_cached_chunks = max_cached_chunks
+        self.first_live_chunk = 0
         self.cache: Optional[ops.ChunkPagedKVCache] = None
+
+    def evict_below(self, chunk_id: int) -> None:
+        """Drop the pages of chunks < chunk_id in every layer.  The reference keeps the whole clip in its flat buffer
+        (max_sequence_length = all tokens, pipeline/video_generate.py:311-314) although the k windows
+        (noise2clean_kvrange / clean_chunk_kvrange, :467-508) never reach back further than a few chunks; with pages,
+        a long clip only needs max_cached_chunks = window + chunks in flight slots per layer."""
+        if self.cache is not None:
+            for c in range(self.first_live_chunk, chunk_id):
+                try:
+                    self.cache.evict(c)
+                except ops.MagiError:  # a chunk that was never stored
+                    pass
+        self.first_live_chunk = max(self.first_live_chunk, chunk_id)
 
     def get_cache(self, chunk_tokens: int, n_kv_heads: int, device) -> ops.ChunkPagedKVCache:
         if self.cache is None:
-            max_chunks = max(1, self.max_sequence_length // chunk_tokens)
+            max_chunks = self.max_cached_chunks or max(1, self.max_sequence_length // chunk_tokens)
             self.cache = ops.ChunkPagedKVCache(self.n_layers, max_chunks, chunk_tokens, n_kv_heads, dtype=self.kv_dtype,
                                                device=device)
         elif self.cache.chunk_tokens != chunk_tokens or self.cache.n_kv_heads != n_kv_heads:
@@ -126,7 +142,8 @@ class ChunkCausalSelfAttention:
         Touches the cache only if extract_prefix_video_feature or fwd_extra_1st_chunk or slice_point > 0.  Then the
         prefix is chunks 0 .. slice_point-1 (read in place by the kernel), and with update_kv_cache the current chunks
         are written to pages slice_point + j - all of them, or all but the last when distill_nearly_clean_chunk.
-        Returns (cache or None, prefix chunk ids); key / value themselves are used as they are."""
+        Returns (cache or None, prefix chunk ids); key / value themselves are used as they are.  After
+        InferenceParams.evict_below(c) the prefix starts at chunk c."""
         if inference_params is None:
             return None, ()
         if not (meta_args.extract_prefix_video_feature or meta_args.fwd_extra_1st_chunk or meta_args.slice_point > 0):
@@ -140,14 +157,22 @@ class ChunkCausalSelfAttention:
             for j in range((n_tok + C - 1) // C):
                 lo, hi = j * C, min((j + 1) * C, n_tok)
                 cache.append(self.layer_number, meta_args.slice_point + j, key[lo:hi], value[lo:hi])
-        return cache, list(range(meta_args.slice_point))
+        return cache, list(range(inference_params.first_live_chunk, meta_args.slice_point))
 
     def core_attention(self, query, key, value, meta_args: ModelMetaArgs, cache=None, prefix_chunk_ids=(),
                        proj_in: Optional[ProjInput] = None):
         """With proj_in the heads are stored at their final columns of the projection operand (proj_in.buf)."""
         p = meta_args.core_attn_params
         dest = proj_in.dest(0) if proj_in is not None else {}
-        out, _ = ops.chunk_attn(query, key, value, p.q_range, p.k_range, p.max_seqlen_q, p.max_seqlen_k, cache=cache,
+        k_range = p.k_range
+        if cache is not None and meta_args.slice_point > len(prefix_chunk_ids):
+            # k_range counts tokens from chunk 0 of the clip (the reference's flat buffer); the page list starts at the
+            # first chunk that is still cached
+            off = (meta_args.slice_point - len(prefix_chunk_ids)) * meta_args.clip_token_nums
+            if int(p.np_k_range.min()) < off:
+                raise ValueError("k_range reaches into chunks that were evicted")
+            k_range = p.k_range - off
+        out, _ = ops.chunk_attn(query, key, value, p.q_range, k_range, p.max_seqlen_q, p.max_seqlen_k, cache=cache,
                                 layer=self.layer_number, prefix_chunk_ids=prefix_chunk_ids, return_lse=False, **dest)
         return proj_in.buf if proj_in is not None else out
 

@@ -79,3 +79,41 @@ def test_denoising_schedule_with_paged_cache_matches_flat_cache_oracle():
         assert (k_page.cpu().float() - flat[..., :128]).abs().max().item() <= 2 ** -5
         assert torch.equal(v_page.cpu().float(), flat[..., 128:])
     ip.cache.close()
+
+
+def test_long_clip_streams_through_a_small_page_pool():
+    """12 chunks with the shipped windows (noise2clean_kvrange [5,4,3,2], clean_chunk_kvrange 1): in the steady state
+    every stage re-forwards the chunk that just became clean together with the four noisy ones, then denoises the four.
+    Chunks behind the widest window are evicted, so 9 page slots per layer serve the whole clip, while the oracle keeps
+    the reference's flat buffer of all 12 chunks.  k-ranges are the reference's absolute token offsets (k-start > 0)."""
+    from magi_b200 import host
+    from magi_b200.inference import ChunkCausalSelfAttention, InferenceParams
+    n_chunks, window = 12, [5, 4, 3, 2]
+    params = host.synthetic_norm_params(62)
+    layer = ChunkCausalSelfAttention(0, HQ, HKV, *params)
+    ip = InferenceParams(max_batch_size=1, max_sequence_length=n_chunks * C, n_layers=1, max_cached_chunks=9)
+    ref_cache = O.RefKVCache(n_chunks * C, HKV)
+    gen = torch.Generator().manual_seed(62)
+    sin_cos = O.rope_table(2 * n_chunks, 10, 13)
+    run = lambda *a, **k: _step(layer, ip, ref_cache, gen, params, sin_cos, *a, **k)
+
+    def noisy_ranges(first, count):
+        return [(max(c + 1 - window[j], 0), c + 1) for j, c in enumerate(range(first, first + count))]
+
+    # fill-up: chunks 0..3 enter one by one (no cache traffic yet), then chunk 0 is finished
+    for s in range(4):
+        run(0, s + 1, [(0, j + 1) for j in range(s + 1)], update=True)
+    for s in range(4, n_chunks + 4):
+        clean = s - 4                                     # the chunk that became clean at the end of the last stage
+        last = min(s, n_chunks - 1)                       # the newest chunk in flight
+        noisy_first = clean + 1
+        n_noisy = last - noisy_first + 1
+        ip.evict_below(max(0, noisy_first + 1 - window[0]))
+        # first step of the stage: the clean chunk is forwarded once more (sees only itself) and stored
+        run(clean, 1 + n_noisy, [(clean, clean + 1)] + noisy_ranges(noisy_first, n_noisy), update=True, extra=True)
+        if n_noisy:
+            run(noisy_first, n_noisy, noisy_ranges(noisy_first, n_noisy), update=True)
+            run(noisy_first, n_noisy, noisy_ranges(noisy_first, n_noisy), update=False)   # the CFG pass
+    assert ip.first_live_chunk == n_chunks + 1 - window[0]
+    assert ip.cache.max_chunks == 9
+    ip.cache.close()
