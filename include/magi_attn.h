@@ -60,6 +60,12 @@ MAGI_API const char* magi_last_error(const magi_ctx* ctx);
 /* Synchronises `stream`, then reads the device status word: 0, MAGI_E_RANGE (plan kernel met an
  * inconsistent range) or MAGI_E_TIMEOUT (a bounded mbarrier wait in a kernel gave up).  Clears the word. */
 MAGI_API int magi_ctx_status(magi_ctx* ctx, void* stream, int* device_status);
+/* Self-test of the device-side failure detection (no reference counterpart).  Every wait inside the attention kernels
+ * is bounded: after a cycle limit the waiting role gives up, the other roles of the CTA follow, the kernel frees what it
+ * holds, returns, and magi_ctx_status reads MAGI_E_TIMEOUT.  This entry runs that same wait on a barrier that nothing
+ * completes, with `limit_cycles` (1e3 .. 2e8 SM cycles) as the limit: the launch returns normally and the status word
+ * reads MAGI_E_TIMEOUT afterwards.  Nothing faults, traps or hangs; the context stays usable. */
+MAGI_API int magi_selftest_bounded_wait(magi_ctx* ctx, long long limit_cycles, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------
  * Prologue: per-head norm + 3D RoPE, fused.  Replaces FullyParallelAttention.get_q / get_k

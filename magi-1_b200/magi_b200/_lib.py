@@ -18,7 +18,7 @@ EXPORTS = [
     "magi_qk_norm_rope_fwd", "magi_head_block_copy", "magi_kv_cache_create", "magi_kv_cache_destroy",
     "magi_kv_cache_append", "magi_kv_cache_evict", "magi_kv_cache_read", "magi_kv_cache_bytes",
     "magi_chunk_attn_fwd", "magi_chunk_attn_fwd_simt", "magi_quantize_e4m3_block128", "magi_chunk_attn_fwd_noalloc",
-    "magi_peer_alloc", "magi_peer_open", "magi_peer_close", "magi_peer_free",
+    "magi_peer_alloc", "magi_peer_open", "magi_peer_close", "magi_peer_free", "magi_selftest_bounded_wait",
 ]
 
 
@@ -77,6 +77,7 @@ def _load():
         "magi_ctx_destroy": (C.c_int, [vp]),
         "magi_last_error": (C.c_char_p, [vp]),
         "magi_ctx_status": (C.c_int, [vp, vp, C.POINTER(C.c_int)]),
+        "magi_selftest_bounded_wait": (C.c_int, [vp, C.c_longlong, vp]),
         "magi_qk_norm_rope_fwd": (C.c_int, [vp, C.POINTER(PrologueParams), vp]),
         "magi_head_block_copy": (C.c_int, [vp, C.POINTER(PrologueParams), vp]),
         "magi_kv_cache_create": (C.c_int, [vp, C.POINTER(KVCacheDesc), C.POINTER(vp)]),

@@ -45,6 +45,11 @@ class Context:
         check(lib.magi_ctx_status(self.handle, _stream(stream), C.byref(st)), self.handle)
         return st.value
 
+    def selftest_bounded_wait(self, limit_cycles: int = 2_000_000, stream=None) -> None:
+        """Run the kernels' bounded mbarrier wait on a barrier that nothing completes (it gives up after limit_cycles);
+        status() must read E_TIMEOUT afterwards.  Nothing faults or hangs."""
+        check(lib.magi_selftest_bounded_wait(self.handle, int(limit_cycles), _stream(stream)), self.handle)
+
     def close(self):
         if self.handle:
             lib.magi_ctx_destroy(self.handle)
