@@ -267,8 +267,11 @@ def chunk_attn(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
         p.total_k, p.n_kv_heads = 0, cache.n_kv_heads
     keep_peers = None
     if o_peers is not None:
-        # fused output exchange: (ptrs per rank, token offsets [cp+1], first global head of this rank, stride_t, stride_h)
-        ptrs, offs, head_off, st_t, st_h = o_peers
+        # fused output exchange: (ptrs per rank, token offsets [cp+1], first global head of this rank, stride_t, stride_h
+        # [, heads per block, block stride] for the head-block layout over the global head index)
+        ptrs, offs, head_off, st_t, st_h = o_peers[:5]
+        if len(o_peers) == 7:
+            p.o_heads_per_block, p.o_stride_block = int(o_peers[5]), int(o_peers[6])
         a_ptrs = (C.c_void_p * len(ptrs))(*[int(a) for a in ptrs])
         a_offs = (C.c_int32 * len(offs))(*[int(o) for o in offs])
         keep_peers = (a_ptrs, a_offs)

@@ -184,7 +184,11 @@ class FusedUlyssesAttention:
     The returned tensor is a view of this object's result buffer and is overwritten by the next call.
     """
 
-    def __init__(self, cp_group, n_q_heads: int, n_kv_heads: int, split_sizes: Sequence[int]):
+    def __init__(self, cp_group, n_q_heads: int, n_kv_heads: int, split_sizes: Sequence[int], proj_hn: int = 0):
+        """proj_hn > 0 (8 in the reference): the result buffer is the operand of the output projection,
+        [s_local, 2 * Hq * 128] in the "(hn n hd)" order of attn_linear_proj (dit_module.py:1332-1346); every rank's
+        epilogue stores its heads at their final columns of the core-attention half, and cross_dest() gives the
+        arguments with which the (rank-local) cross-attention call fills the other half."""
         from . import ops
         self.ops = ops
         self.group = cp_group
@@ -209,7 +213,11 @@ class FusedUlyssesAttention:
         dev = torch.cuda.current_device()
         self.buf_q = ops.PeerBuffer(S * self.hq_loc * HEAD_DIM * 2, dev)
         self.buf_kv = ops.PeerBuffer(S * self.hkv_loc * 2 * HEAD_DIM * 2, dev)
-        self.buf_o = ops.PeerBuffer(s_max * self.hq * HEAD_DIM * 2, dev)
+        if proj_hn and n_q_heads % proj_hn:
+            raise ValueError("the head count must be a multiple of proj_hn")
+        self.proj_hn = int(proj_hn)
+        self.o_row = (2 if proj_hn else 1) * self.hq * HEAD_DIM   # elements per token in a result buffer
+        self.buf_o = ops.PeerBuffer(s_max * self.o_row * 2, dev)
         handles = [None] * cp
         dist.all_gather_object(handles, (self.buf_q.handle, self.buf_kv.handle, self.buf_o.handle), group=cp_group)
         self.peer_q, self.peer_kv, self.peer_o = [], [], []
@@ -224,7 +232,7 @@ class FusedUlyssesAttention:
         self._flag = torch.zeros(1, dtype=torch.float32, device=torch.device("cuda", dev))
         self.q_recv = self.buf_q.as_tensor((S, self.hq_loc, HEAD_DIM))
         self.kv_recv = self.buf_kv.as_tensor((S, self.hkv_loc, 2 * HEAD_DIM))
-        self.out = self.buf_o.as_tensor((s_max, self.hq, HEAD_DIM))
+        self.out = self.buf_o.as_tensor((s_max, self.o_row) if proj_hn else (s_max, self.hq, HEAD_DIM))
         self._barrier()
 
     def _barrier(self):
@@ -250,12 +258,21 @@ class FusedUlyssesAttention:
         ops.chunk_attn(self.q_recv, self.kv_recv[..., :HEAD_DIM], self.kv_recv[..., HEAD_DIM:], q_ranges, k_ranges, max_seqlen_q,
                        max_seqlen_k, return_lse=False, k_range_offsets=k_range_offsets, cache=cache, layer=layer,
                        prefix_chunk_ids=prefix_chunk_ids,
-                       o_peers=(self.peer_o, self.offsets, self.rank * self.hq_loc, self.hq * HEAD_DIM, HEAD_DIM))
+                       o_peers=(self.peer_o, self.offsets, self.rank * self.hq_loc, self.o_row, HEAD_DIM) + (
+                           (self.hq // self.proj_hn, 2 * (self.hq // self.proj_hn) * HEAD_DIM) if self.proj_hn else ()))
         if attn_events is not None:
             e1.record()
             attn_events.append((e0, e1))
         self._barrier()  # every rank's output rows have landed in every result buffer
         return self.out[:self.s_loc]
+
+    def cross_dest(self) -> dict:
+        """chunk_attn keyword arguments that store this rank's cross-attention heads into the other half of the
+        projection operand (proj_hn > 0)."""
+        if not self.proj_hn:
+            raise ValueError("created without proj_hn")
+        hd = (self.hq // self.proj_hn) * HEAD_DIM
+        return dict(out=self.out[:self.s_loc, hd:], out_heads_per_block=self.hq // self.proj_hn, out_block_stride=2 * hd)
 
     def close(self):
         torch.cuda.synchronize()

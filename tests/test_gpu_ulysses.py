@@ -18,7 +18,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, overlap, fp8=False, fused=False):
+def _worker(rank, world, port, overlap, fp8=False, fused=False, proj=False):
     for p in (ROOT, os.path.join(ROOT, "magi-1_b200"), os.path.join(ROOT, "tests")):
         if p not in sys.path:
             sys.path.insert(0, p)
@@ -44,7 +44,7 @@ def _worker(rank, world, port, overlap, fp8=False, fused=False):
     off = sum(splits[:rank])
     sl = slice(off, off + splits[rank])
     qr, kr = host.q_ranges_for_chunks(n, C), host.default_k_ranges(n, C)
-    ua = FusedUlyssesAttention(dist.group.WORLD, Hq, Hkv, splits) if fused else \
+    ua = FusedUlyssesAttention(dist.group.WORLD, Hq, Hkv, splits, proj_hn=8 if proj else 0) if fused else \
         UlyssesAttention(dist.group.WORLD, Hq, Hkv, splits, overlap_degree=overlap)
     dev = torch.device("cuda", rank)
     for _ in range(2):  # second pass reuses the buffers
@@ -58,7 +58,25 @@ def _worker(rank, world, port, overlap, fp8=False, fused=False):
     k_ref = O.qk_prologue(xk, gk, bk, cos, sin).float()
     rows, ref, _ = oracle_on_rows(q_ref, k_ref, xv.float(), qr, as_segments(kr), torch.arange(off, off + splits[rank]))
     assert torch.equal(rows, torch.arange(off, off + splits[rank]))
-    if fp8:
+    if proj:
+        # the result buffer is the projection operand: core heads at their "(hn n hd)" columns, and the rank-local
+        # cross-attention fills the other half in place
+        from magi_b200.inference import ProjInput
+        caps = [50, 0, 120]
+        yk = torch.randn(sum(caps), Hkv, 128, generator=g).to(torch.bfloat16).to(dev)
+        yv = torch.randn(sum(caps), Hkv, 128, generator=g).to(torch.bfloat16).to(dev)
+        xqr, xkr = host.cross_attn_ranges(C, n, caps)
+        ql, kl, max_q = host.cp_cross_attn_ranges(xqr, xkr, splits, rank)
+        q_loc = q_ref[sl].to(torch.bfloat16).to(dev)
+        cross, _ = mb.chunk_attn(q_loc, yk, yv, ql, kl, max_q, max(caps))
+        mb.chunk_attn(q_loc, yk, yv, ql, kl, max_q, max(caps), return_lse=False, **ua.cross_dest())
+        torch.cuda.synchronize()
+        assert out.shape == (splits[rank], 2 * Hq * 128)
+        core_cols = torch.arange(2 * Hq * 128).view(8, 2, -1)[:, 0].reshape(-1).to(dev)
+        core = out[:, core_cols].reshape(splits[rank], Hq, 128)
+        assert_close(core, ref, what=f"fused ulysses cp{world} rank {rank}, projection layout")
+        assert torch.equal(out, ProjInput.reference_layout(core, cross))
+    elif fp8:
         assert O.cosine(out.cpu(), ref) >= 0.999, O.cosine(out.cpu(), ref)
     else:
         assert_close(out, ref, what=f"ulysses cp{world} rank {rank}")
@@ -76,6 +94,14 @@ def test_fused_peer_memory_exchange_matches_oracle(world):
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     mp.spawn(_worker, args=(world, _free_port(), 1, False, True), nprocs=world, join=True)
+
+
+def test_fused_exchange_writes_the_projection_operand():
+    """attn_linear_proj's cat + rearrange (dit_module.py:1332-1346) folded into the fused output exchange."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(2, _free_port(), 1, False, True, True), nprocs=2, join=True)
 
 
 @pytest.mark.parametrize("world,overlap", [(2, 1), (2, 2), (4, 1)])
