@@ -23,6 +23,7 @@ namespace magi {
 using namespace ptx;
 
 constexpr int kAttnThreads = 384;
+constexpr float kRedoRowSum = 32768.0f;  // 128 columns * 2^8: the fast path is redone for any row sum above this
 constexpr int kTileBytes = kTileN * kHeadDim * 2;  // 32768: one 128x128 bf16 tile
 constexpr int kHalfBytes = kTileBytes / 2;         // a [128 x 64] half tile = one 128-byte-swizzled TMA box
 constexpr uint32_t kSw128 = 2;
@@ -315,23 +316,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         float alpha = 1.0f, rowsum = 0.f;
         bool redo = (j == 0);
         if (j > 0) {
-          // Fast path: exponentials against the maximum already baked into O and l, the tile's own maximum computed
-          // alongside (8 + 4 independent chains keep the MUFU pipe fed).  If the maximum turns out to have grown by
-          // more than 2^8 for any row of the warp, the tile is redone below from the S still held in TMEM.
+          // Fast path: exponentials against the maximum already baked into O and l; no maximum is computed.  A row
+          // whose scores outgrew that reference shows in its row sum: above 128 * 2^8 (some weight is then above 2^8;
+          // inf and NaN also land here) the tile is redone below from the S still held in TMEM.
           const float neg_m = -m_used * sl2;
-          float mxa[8], rs[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int c = 0; c < 8; ++c) mxa[c] = __uint_as_float(s[c]);
+          float rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int c = 0; c < kTileN; c += 4) {
-            const float s0 = __uint_as_float(s[c]), s1 = __uint_as_float(s[c + 1]);
-            const float s2 = __uint_as_float(s[c + 2]), s3 = __uint_as_float(s[c + 3]);
-            mxa[c & 7] = fmaxf(mxa[c & 7], s0);
-            mxa[(c + 1) & 7] = fmaxf(mxa[(c + 1) & 7], s1);
-            mxa[(c + 2) & 7] = fmaxf(mxa[(c + 2) & 7], s2);
-            mxa[(c + 3) & 7] = fmaxf(mxa[(c + 3) & 7], s3);
-            const float p0 = ex2(fmaf(s0, sl2, neg_m)), p1 = ex2(fmaf(s1, sl2, neg_m));
-            const float p2 = ex2(fmaf(s2, sl2, neg_m)), p3 = ex2(fmaf(s3, sl2, neg_m));
+            const float p0 = ex2(fmaf(__uint_as_float(s[c]), sl2, neg_m));
+            const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), sl2, neg_m));
+            const float p2 = ex2(fmaf(__uint_as_float(s[c + 2]), sl2, neg_m));
+            const float p3 = ex2(fmaf(__uint_as_float(s[c + 3]), sl2, neg_m));
             rs[0] += p0;
             rs[1] += p1;
             rs[2] += p2;
@@ -339,10 +334,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             s[c >> 1] = pack_bf16x2(p0, p1);
             s[(c >> 1) + 1] = pack_bf16x2(p2, p3);
           }
-          const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
-                                 fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
           rowsum = (rs[0] + rs[2]) + (rs[1] + rs[3]);
-          redo = __any_sync(0xffffffffu, (mx - m_used) * sl2 > 8.0f);
+          redo = __any_sync(0xffffffffu, !(rowsum <= kRedoRowSum));
           if (redo) load_s();
         }
         if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 3);
