@@ -263,7 +263,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           MAGI_STAMP(0, j, 4 * x + 1);
           tc_fence_after_sync();
           issue_pv(x, v_stage, j == 0);
-          umma_commit(&o_full[x]);
+          if (!more) umma_commit(&o_full[x]);  // only the epilogue waits for O (a later S_x implies the earlier PV_x)
           if (x == 1) umma_commit(&kv_empty[v_stage]);
           if (more) {
             issue_qk(x, k_stage);
@@ -318,23 +318,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (j > 0) {
           // Fast path: exponentials against the maximum already baked into O and l; no maximum is computed.  A row
           // whose scores outgrew that reference shows in its row sum: above 128 * 2^8 (some weight is then above 2^8;
-          // inf and NaN also land here) the tile is redone below from the S still held in TMEM.
+          // inf and NaN also land here) the tile is redone below from the S still held in TMEM.  Scale-and-subtract
+          // and the row sum run as packed fp32 pairs (half the instructions; the chain is issue-bound, not MUFU-bound).
           const float neg_m = -m_used * sl2;
-          float rs[4] = {0.f, 0.f, 0.f, 0.f};
+          uint64_t rs01 = f2_pack(0.f, 0.f), rs23 = rs01;
+          const uint64_t sl2_2 = f2_pack(sl2, sl2), neg_m2 = f2_pack(neg_m, neg_m);
 #pragma unroll
           for (int c = 0; c < kTileN; c += 4) {
-            const float p0 = ex2(fmaf(__uint_as_float(s[c]), sl2, neg_m));
-            const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), sl2, neg_m));
-            const float p2 = ex2(fmaf(__uint_as_float(s[c + 2]), sl2, neg_m));
-            const float p3 = ex2(fmaf(__uint_as_float(s[c + 3]), sl2, neg_m));
-            rs[0] += p0;
-            rs[1] += p1;
-            rs[2] += p2;
-            rs[3] += p3;
+            float x0, x1, x2, x3;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sl2_2, neg_m2), x0, x1);
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), sl2_2, neg_m2), x2, x3);
+            const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(x2), p3 = ex2(x3);
+            rs01 = f2_add(rs01, f2_pack(p0, p1));
+            rs23 = f2_add(rs23, f2_pack(p2, p3));
             s[c >> 1] = pack_bf16x2(p0, p1);
             s[(c >> 1) + 1] = pack_bf16x2(p2, p3);
           }
-          rowsum = (rs[0] + rs[2]) + (rs[1] + rs[3]);
+          {
+            float r0, r1, r2, r3;
+            f2_unpack(rs01, r0, r1);
+            f2_unpack(rs23, r2, r3);
+            rowsum = (r0 + r2) + (r1 + r3);
+          }
           redo = __any_sync(0xffffffffu, !(rowsum <= kRedoRowSum));
           if (redo) load_s();
         }
@@ -393,7 +398,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 6);
       }
     }
-    if (ok) ok = mbar_wait(&o_full[x], (n_tiles - 1) & 1, abort_flag);
+    if (ok) ok = mbar_wait(&o_full[x], 0, abort_flag);
     if (ok) {
       tc_fence_after_sync();
       const int r_in_item = x * kTileM + row;
