@@ -196,7 +196,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           if (!ok) break;
           tc_fence_after_sync();
           issue_pv(x, j);
-          umma_commit(&o_full[x]);
+          if (!more) umma_commit(&o_full[x]);  // only the epilogue waits for O
           if (x == 1) umma_commit(&kv_empty[stage_of(2 * j + 1)]);
           if (more) {
             issue_qk(x, j + 1);
@@ -288,9 +288,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           }
         }
         if (j > 0) {
-          ok = mbar_wait(&o_full[x], (j - 1) & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after_sync();
+          // S_x(j) complete implies PV_x(j-1) complete (same issuing thread, in order), so O_x may be rescaled here
           if (__any_sync(0xffffffffu, need)) {
 #pragma unroll 1
             for (int c4 = 0; c4 < 4; ++c4) {
@@ -311,7 +309,7 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (lane == 0) mbar_arrive(&p_full[x]);
       }
     }
-    if (ok) ok = mbar_wait(&o_full[x], (n_tiles - 1) & 1, abort_flag);
+    if (ok) ok = mbar_wait(&o_full[x], 0, abort_flag);
     if (ok) {
       tc_fence_after_sync();
       const int r_in_item = x * kTileM + row;
