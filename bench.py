@@ -28,12 +28,12 @@ WORKLOADS = {
     # 24B-style 720p layer: 48/8 heads, 45x80 patches x 6 frames per chunk, 4 chunks, block-causal (cfg 3)
     "cfg3": dict(name="24B-720p: Hq48/Hkv8 d128, 4 chunks x 21600 tok (T24 H45 W80), block-causal, bf16",
                  hq=48, hkv=8, H=45, W=80, frames_per_chunk=6, n_chunks=4, seed=3,
-                 # dram__bytes_read+write of attn_fwd_kernel per launch: ncu capture of the cfg1 launch (589.2 MB)
+                 # dram__bytes_read+write of attn_fwd_kernel per launch: ncu capture of the cfg1 launch (592.5 MB)
                  # scaled by the bytes the launch processes (x 2477.3 / 613.4)
-                 traffic_bytes=2379.6e6),
+                 traffic_bytes=2392.9e6),
     # 4.5B-style layer: 24/8 heads, 30x52 patches x 6 frames per chunk, 4 chunks (cfg 1)
     "cfg1": dict(name="4.5B-style: Hq24/Hkv8 d128, 4 chunks x 9360 tok (T24 H30 W52), block-causal, bf16",
-                 hq=24, hkv=8, H=30, W=52, frames_per_chunk=6, n_chunks=4, seed=1, traffic_bytes=589.2e6),
+                 hq=24, hkv=8, H=30, W=52, frames_per_chunk=6, n_chunks=4, seed=1, traffic_bytes=592.5e6),
     # KV-cache decode step (cfg 2): batch 2 (CFG), 4 denoising chunks each, chunk i sees its own cached prefix of i chunks + itself
     "cfg2": dict(name="4.5B-style decode: b2 x 4 denoising chunks x 9360 tok, own paged bf16 prefix (0..3 chunks) + self",
                  hq=24, hkv=8, H=30, W=52, frames_per_chunk=6, n_chunks=4, seed=2, decode=True, batch=2, n_prefix=3),
