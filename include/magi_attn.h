@@ -253,6 +253,28 @@ MAGI_API int magi_peer_free(magi_ctx* ctx, void* dev_ptr);
 MAGI_API int magi_quantize_e4m3_block128(magi_ctx* ctx, const void* x, int64_t stride_t, int64_t stride_h, int T, int H,
                                 int chunk_tokens, void* x8, void* x8_lo, float* scales, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------
+ * Ulysses head-split exchange on a communicator the library owns, for hosts that do not route their collectives through
+ * torch.distributed.  Replaces all_to_all_input_split / all_to_all_output_split
+ * (inference/infra/parallelism/context_parallel.py:381-401, :404-423): grouped ncclSend / ncclRecv with the uneven
+ * contiguous sequence split of cp_ulysses_process (:227-254).  NCCL is resolved at run time from the libnccl.so.2 already
+ * in the process; without it these entry points return MAGI_E_NCCL.  All calls are stream-ordered on `stream`.
+ *   magi_ulysses_unique_id: on one rank; the caller distributes the 128 bytes (as the reference's launcher does with
+ *                           its rendezvous) and every rank passes them to magi_ulysses_create (collective).
+ *   split_sizes:            HOST int32 [cp], tokens per rank; rank r owns rows [sum(split[:r]), +split[r]).
+ *   a2a_in  ("scatter heads"): send [cp, s_local, row_bytes] (block r = the heads of rank r, as the prologue writes it
+ *                           with heads_per_block) -> recv [s_total, row_bytes] (all tokens, own heads).
+ *   a2a_out ("gather heads"):  full [s_total, row_bytes] -> recv [cp, s_local, row_bytes]; magi_head_block_copy then
+ *                           gives "(cp sq) hn hd -> sq (cp hn) hd" (:596).
+ */
+typedef struct magi_ulysses magi_ulysses;
+MAGI_API int magi_ulysses_unique_id(magi_ctx* ctx, void* id128);
+MAGI_API int magi_ulysses_create(magi_ctx* ctx, const void* id128, int rank, int cp, const int32_t* split_sizes,
+                                 magi_ulysses** out);
+MAGI_API int magi_ulysses_destroy(magi_ulysses* u);
+MAGI_API int magi_ulysses_a2a_in(magi_ulysses* u, const void* send, void* recv, int64_t row_bytes, void* stream);
+MAGI_API int magi_ulysses_a2a_out(magi_ulysses* u, const void* full, void* recv, int64_t row_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -19,6 +19,7 @@ EXPORTS = [
     "magi_kv_cache_append", "magi_kv_cache_evict", "magi_kv_cache_read", "magi_kv_cache_bytes",
     "magi_chunk_attn_fwd", "magi_chunk_attn_fwd_simt", "magi_quantize_e4m3_block128", "magi_chunk_attn_fwd_noalloc",
     "magi_peer_alloc", "magi_peer_open", "magi_peer_close", "magi_peer_free", "magi_selftest_bounded_wait",
+    "magi_ulysses_unique_id", "magi_ulysses_create", "magi_ulysses_destroy", "magi_ulysses_a2a_in", "magi_ulysses_a2a_out",
 ]
 
 
@@ -78,6 +79,11 @@ def _load():
         "magi_last_error": (C.c_char_p, [vp]),
         "magi_ctx_status": (C.c_int, [vp, vp, C.POINTER(C.c_int)]),
         "magi_selftest_bounded_wait": (C.c_int, [vp, C.c_longlong, vp]),
+        "magi_ulysses_unique_id": (C.c_int, [vp, vp]),
+        "magi_ulysses_create": (C.c_int, [vp, vp, i32, i32, C.POINTER(C.c_int32), C.POINTER(vp)]),
+        "magi_ulysses_destroy": (C.c_int, [vp]),
+        "magi_ulysses_a2a_in": (C.c_int, [vp, vp, vp, i64, vp]),
+        "magi_ulysses_a2a_out": (C.c_int, [vp, vp, vp, i64, vp]),
         "magi_qk_norm_rope_fwd": (C.c_int, [vp, C.POINTER(PrologueParams), vp]),
         "magi_head_block_copy": (C.c_int, [vp, C.POINTER(PrologueParams), vp]),
         "magi_kv_cache_create": (C.c_int, [vp, C.POINTER(KVCacheDesc), C.POINTER(vp)]),

@@ -54,6 +54,63 @@ class UlyssesExchange:
         return recv, work
 
 
+class _Done:
+    """Stand-in for a torch.distributed work handle: the C-level exchange is ordered on the current stream."""
+
+    def wait(self):
+        return True
+
+
+class LibraryExchange(UlyssesExchange):
+    """The same two all-to-alls through the library's own NCCL communicator (magi_ulysses_*), i.e. the path a host
+    without torch.distributed would take; torch.distributed is used here only to hand the 128-byte unique id around.
+    Calls are ordered on the current CUDA stream."""
+
+    def __init__(self, group, split_sizes: Sequence[int]):
+        super().__init__(group, split_sizes)
+        import ctypes as C
+        from . import ops
+        from ._lib import check, lib
+        self._C, self._lib, self._check, self._ops = C, lib, check, ops
+        self.ctx = ops.Context.get(torch.cuda.current_device())
+        uid = C.create_string_buffer(128)
+        if self.rank == 0:
+            check(lib.magi_ulysses_unique_id(self.ctx.handle, uid), self.ctx.handle)
+        box = [uid.raw]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0), group=group)
+        uid = C.create_string_buffer(box[0], 128)
+        sizes = (C.c_int32 * self.cp)(*self.split_sizes)
+        h = C.c_void_p()
+        check(lib.magi_ulysses_create(self.ctx.handle, uid, self.rank, self.cp, sizes, C.byref(h)), self.ctx.handle)
+        self.handle = h
+
+    def scatter_heads(self, send: torch.Tensor, recv: Optional[torch.Tensor] = None, async_op: bool = True):
+        if send.shape[0] != self.cp or send.shape[1] != self.s_local or not send.is_contiguous():
+            raise ValueError(f"send must be contiguous [cp={self.cp}, s_local={self.s_local}, hn, d], got {tuple(send.shape)}")
+        if recv is None:
+            recv = torch.empty((self.s_total,) + tuple(send.shape[2:]), dtype=send.dtype, device=send.device)
+        row_bytes = send[0, 0].numel() * send.element_size()
+        self._check(self._lib.magi_ulysses_a2a_in(self.handle, send.data_ptr(), recv.data_ptr(), row_bytes,
+                                                  self._ops._stream()), self.ctx.handle)
+        return recv, _Done()
+
+    def gather_heads(self, full: torch.Tensor, recv: Optional[torch.Tensor] = None, async_op: bool = True):
+        if full.shape[0] != self.s_total or not full.is_contiguous():
+            raise ValueError(f"full must be contiguous [s_total={self.s_total}, hn, d], got {tuple(full.shape)}")
+        if recv is None:
+            recv = torch.empty((self.cp, self.s_local) + tuple(full.shape[1:]), dtype=full.dtype, device=full.device)
+        row_bytes = full[0].numel() * full.element_size()
+        self._check(self._lib.magi_ulysses_a2a_out(self.handle, full.data_ptr(), recv.data_ptr(), row_bytes,
+                                                   self._ops._stream()), self.ctx.handle)
+        return recv, _Done()
+
+    def close(self):
+        if getattr(self, "handle", None):
+            torch.cuda.synchronize()
+            self._lib.magi_ulysses_destroy(self.handle)
+            self.handle = None
+
+
 def kv_head_replication(n_kv_heads: int, cp: int) -> int:
     """KV heads are repeated when there are more ranks than heads (context_parallel.py:393-394)."""
     if cp % n_kv_heads == 0 and cp != n_kv_heads and cp > n_kv_heads:
@@ -66,10 +123,12 @@ def kv_head_replication(n_kv_heads: int, cp: int) -> int:
 class UlyssesAttention:
     """Prologue + exchange + attention + exchange for one layer on one CP rank (CUDA)."""
 
-    def __init__(self, cp_group, n_q_heads: int, n_kv_heads: int, split_sizes: Sequence[int], overlap_degree: int = 1):
+    def __init__(self, cp_group, n_q_heads: int, n_kv_heads: int, split_sizes: Sequence[int], overlap_degree: int = 1,
+                 exchange: str = "torch"):
+        """exchange = "torch": torch.distributed all_to_all_single; "library": the library's own NCCL communicator."""
         from . import ops
         self.ops = ops
-        self.ex = UlyssesExchange(cp_group, split_sizes)
+        self.ex = {"torch": UlyssesExchange, "library": LibraryExchange}[exchange](cp_group, split_sizes)
         cp = self.ex.cp
         if n_q_heads % cp:
             raise ValueError(f"{n_q_heads} q heads cannot be split over {cp} ranks")

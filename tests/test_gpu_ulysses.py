@@ -18,7 +18,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, overlap, fp8=False, fused=False, proj=False):
+def _worker(rank, world, port, overlap, fp8=False, fused=False, proj=False, exchange="torch"):
     for p in (ROOT, os.path.join(ROOT, "magi-1_b200"), os.path.join(ROOT, "tests")):
         if p not in sys.path:
             sys.path.insert(0, p)
@@ -45,7 +45,7 @@ def _worker(rank, world, port, overlap, fp8=False, fused=False, proj=False):
     sl = slice(off, off + splits[rank])
     qr, kr = host.q_ranges_for_chunks(n, C), host.default_k_ranges(n, C)
     ua = FusedUlyssesAttention(dist.group.WORLD, Hq, Hkv, splits, proj_hn=8 if proj else 0) if fused else \
-        UlyssesAttention(dist.group.WORLD, Hq, Hkv, splits, overlap_degree=overlap)
+        UlyssesAttention(dist.group.WORLD, Hq, Hkv, splits, overlap_degree=overlap, exchange=exchange)
     dev = torch.device("cuda", rank)
     for _ in range(2):  # second pass reuses the buffers
         out = ua.forward(xq[sl].to(dev), xk[sl].to(dev), xv[sl].to(dev), gq, bq, gk, bk, cos[sl], sin[sl],
@@ -83,6 +83,8 @@ def _worker(rank, world, port, overlap, fp8=False, fused=False, proj=False):
     if fused:
         out = out.clone()
         ua.close()
+    elif exchange == "library":
+        ua.ex.close()
     dist.barrier()
     dist.destroy_process_group()
 
@@ -110,6 +112,14 @@ def test_ulysses_attention_matches_oracle(world, overlap):
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     mp.spawn(_worker, args=(world, _free_port(), overlap), nprocs=world, join=True)
+
+
+def test_exchange_through_the_library_owned_communicator():
+    """magi_ulysses_* (grouped ncclSend / ncclRecv on a communicator created from a broadcast unique id)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(2, _free_port(), 2, False, False, False, "library"), nprocs=2, join=True)
 
 
 def test_ulysses_fp8_attention_matches_oracle():
