@@ -170,6 +170,31 @@ def test_large_magnitude_scores_stay_finite(mb):
     assert torch.allclose(lse.cpu(), ref_lse, atol=5e-2, rtol=1e-3)
 
 
+@pytest.mark.parametrize("step", [0.5, 2.0, 9.0, 40.0])
+def test_reference_maximum_keeps_growing_tile_after_tile(mb, step):
+    """Keys whose scores climb by about `step` (in log2 units of the softmax weights) from one 128-token tile to the
+    next: below the redo threshold the stale reference carries weights far above 1 for many tiles, above it every tile
+    is redone and O rescaled, and the largest step moves the reference by more than fp32 can hold in one weight."""
+    g = torch.Generator().manual_seed(41)
+    T, n_tiles = 128 * 12, 12
+    q = torch.randn(T, 2, 128, generator=g)
+    k = torch.randn(T, 2, 128, generator=g)
+    v = torch.randn(T, 2, 128, generator=g)
+    # add a component along a fixed direction u to q and, growing with the tile index, to k: q.k gains ~ |u|^2 a_q a_k(tile)
+    u = torch.randn(128, generator=g)
+    u = u / u.norm()
+    q = q + 8.0 * u
+    scale_log2 = 1.4426950408889634 / 128 ** 0.5
+    ramp = torch.arange(n_tiles).repeat_interleave(128).float() * (step / (8.0 * scale_log2))
+    k = k + ramp[:, None, None] * u
+    qr = np.array([[0, T]], dtype=np.int32)
+    out, lse, (qb, kb, vb) = _run(mb, q, k, v, qr, qr, T)
+    ref, ref_lse = O.range_attention(qb, kb, vb, qr, as_segments(qr))
+    assert torch.isfinite(out.float()).all()
+    assert_close(out, ref, what=f"growing maximum, step {step}")
+    assert torch.allclose(lse.cpu(), ref_lse, atol=5e-2, rtol=1e-3)
+
+
 def test_cfg1_shape_sampled_rows_and_properties(mb):
     """The 4.5B-style single-GPU benchmark shape: 24/8 heads, 4 chunks of 9360 tokens, block-causal."""
     C, n, Hq, Hkv = 9360, 4, 24, 8
