@@ -57,3 +57,69 @@ def test_cross_attention_range_helpers():
     assert ql.tolist() == [[0, 2], [2, 8]] and kl.tolist() == [[0, 4], [4, 4]] and mq == 8
     ql, kl, mq = host.cp_cross_attn_ranges(qr, kr, splits, 3)     # rows 23..30: inside chunk 2
     assert ql.tolist() == [[0, 7]] and kl.tolist() == [[4, 11]] and mq == 7
+
+
+def test_projection_operand_layout_is_the_reference_rearrange():
+    """ProjInput's column map against the reference's own two lines (attn_linear_proj, dit_module.py:1336-1338):
+    torch.concat(dim=2) followed by einops "sq b (n hn hd) -> sq b (hn n hd)", n=2, hn=8."""
+    from einops import rearrange
+    from magi_b200.inference import ProjInput
+    sq, H = 5, 16
+    core = torch.arange(sq * H * 128, dtype=torch.float32).view(sq, H, 128)
+    cross = -core - 1
+    want = rearrange(torch.concat([core.view(sq, 1, -1), cross.view(sq, 1, -1)], dim=2), "sq b (n hn hd) -> sq b (hn n hd)", n=2, hn=8)
+    got = ProjInput.reference_layout(core, cross)
+    assert torch.equal(got, want.view(sq, -1))
+    # the kernel-side formula: head h of output `which` starts at (h // hpb) * 2 * hd + which * hd + (h % hpb) * 128
+    hpb = H // 8
+    hd = hpb * 128
+    for which, src in ((0, core), (1, cross)):
+        for h in range(H):
+            col = (h // hpb) * 2 * hd + which * hd + (h % hpb) * 128
+            assert torch.equal(got[:, col:col + 128], src[:, h])
+
+
+def test_eviction_horizon_bookkeeping_and_k_range_rebasing():
+    """InferenceParams.evict_below + the layer mirror's prefix list and k-range offset, with a stand-in for the cache."""
+    from magi_b200 import inference as inf
+
+    class FakeCache:
+        chunk_tokens, n_kv_heads = 10, 2
+
+        def __init__(self):
+            self.pages, self.evicted = set(), []
+
+        def append(self, layer, chunk_id, k, v):
+            self.pages.add(chunk_id)
+
+        def evict(self, chunk_id):
+            if chunk_id not in self.pages:
+                raise inf.ops.MagiError(-4, "not cached")
+            self.pages.remove(chunk_id)
+            self.evicted.append(chunk_id)
+
+    ip = inf.InferenceParams(max_batch_size=1, max_sequence_length=120, n_layers=1, max_cached_chunks=6)
+    ip.cache = FakeCache()
+    ip.update_kv_cache = True
+    layer = inf.ChunkCausalSelfAttention(0, 4, 2, None, None, None, None)
+    qr = np.array([[0, 10], [10, 20]], dtype=np.int32)
+    kr = np.array([[30, 60], [40, 70]], dtype=np.int32)          # absolute tokens: chunks 3..5 and 4..6
+    params = inf.PackedCoreAttnParams(torch.as_tensor(qr), torch.as_tensor(kr), qr, kr, 10, 40)
+    meta = inf.ModelMetaArgs(slice_point=5, denoising_range_num=2, clip_token_nums=10, core_attn_params=params)
+    key = torch.zeros(20, 2, 128)
+    for c in range(5):
+        ip.cache.append(0, c, None, None)
+    cache, prefix = layer.adjust_key_and_value_for_inference(key, key, ip, meta)
+    assert prefix == [0, 1, 2, 3, 4] and ip.cache.pages == {0, 1, 2, 3, 4, 5, 6}     # current chunks stored at 5, 6
+    ip.evict_below(3)
+    ip.evict_below(2)                                              # going back is a no-op
+    assert ip.first_live_chunk == 3 and ip.cache.evicted == [0, 1, 2]
+    cache, prefix = layer.adjust_key_and_value_for_inference(key, key, ip, meta)
+    assert prefix == [3, 4]
+    # the k-range offset the attention call will use: (slice_point - len(prefix)) chunks
+    assert (meta.slice_point - len(prefix)) * meta.clip_token_nums == 30 <= int(params.np_k_range.min())
+    ip.evict_below(4)                                              # now the first window reaches an evicted chunk
+    cache, prefix = layer.adjust_key_and_value_for_inference(key, key, ip, meta)
+    import pytest
+    with pytest.raises(ValueError):
+        layer.core_attention(key, key, key, meta, cache, prefix)
