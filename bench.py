@@ -1,7 +1,7 @@
 """Benchmark of the chunk-causal attention hot path (prologue -> [Ulysses in] -> attention -> [Ulysses out]).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3|cfg1|cfg2|cfg4] [--exchange fused|nccl]
-                    [--impl ours|reference] [--no-e2e] [--no-cpu-baseline] [--no-gpu-dispatch-baseline]
+                    [--impl ours|reference] [--no-e2e] [--no-cpu-baseline] [--gpu-dispatch-baseline]
 
 One process per GPU (under torchrun for N > 1; RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the environment).
 Rank 0 prints ONE JSON line.  A "step" is one pass of the hot path over one batch of seeded synthetic inputs of
@@ -170,7 +170,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--no-gpu-dispatch-baseline", action="store_true")
+    ap.add_argument("--gpu-dispatch-baseline", action="store_true",
+                    help="also time the reference's flash_attn_func fallback loop on this GPU (comparison only; loads flash-attn)")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: Ulysses exchange fused into the kernels over peer memory, or NCCL all-to-all + copies")
     args = ap.parse_args()
@@ -413,11 +414,12 @@ def main():
                "h2d_bytes_per_step": h2d * cp, "d2h_bytes_per_step": ho.numel() * 2 * cp,
                "pipeline": "copies overlapped with the neighbouring steps on side streams" if pipelined else "sequential"}
 
-    # ---- secondary baseline, comparison only: the reference's fallback dispatch on this GPU, a loop of flash_attn_func
-    # over the ranges (inference/model/dit/dit_module.py:1049-1065) with the flash-attn build of the image, on the same
-    # prologued Q/K and V.  Never a dispatch target of the library; absent or failing flash-attn leaves the field null.
+    # ---- secondary baseline, on request and for comparison only: the reference's fallback dispatch on this GPU, a loop
+    # of flash_attn_func over the ranges (inference/model/dit/dit_module.py:1049-1065) with the flash-attn build of the
+    # image, on the same prologued Q/K and V, after all of this build's own timing is done.  Never a dispatch target of
+    # the library; flash-attn is not even imported unless the flag is given.
     gpu_dispatch = None
-    if cp == 1 and not args.no_gpu_dispatch_baseline and not w.get("fp8") and not w.get("decode"):
+    if cp == 1 and args.gpu_dispatch_baseline and not w.get("fp8") and not w.get("decode"):
         try:
             import flash_attn
             qr_h, kr_h = qr.cpu().numpy(), kr.cpu().numpy()
