@@ -1,5 +1,7 @@
 """Property test: random head geometry, ragged q-ranges with gaps, one or several k intervals per q-range (windows with
 k-start > 0, lengths that are not multiples of 128, Lq != Lk, empty k) against the CPU oracle and the diagnostic twin."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -27,17 +29,18 @@ def problems(draw):
         cuts = sorted(draw(st.lists(st.integers(0, tk), min_size=2 * m, max_size=2 * m)))
         ivals = [[cuts[2 * i], cuts[2 * i + 1]] for i in range(m)]   # disjoint, ordered, possibly empty intervals
         segs.append(ivals)
-    return hkv, group, tk, pos + draw(st.integers(0, 30)), q_ranges, segs, draw(st.integers(0, 2 ** 31 - 1))
+    amp = draw(st.sampled_from([1.0, 3.0, 10.0]))            # larger scores: the reference maximum moves more often
+    return hkv, group, tk, pos + draw(st.integers(0, 30)), q_ranges, segs, draw(st.integers(0, 2 ** 31 - 1)), amp
 
 
-@settings(max_examples=30, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.data_too_large])
+@settings(max_examples=int(os.environ.get("MAGI_PROPERTY_EXAMPLES", "30")), deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.data_too_large])
 @given(problems())
 def test_random_rectangles_match_oracle(prob):
     import magi_b200 as mb
-    hkv, group, tk, tq, q_ranges, segs, seed = prob
+    hkv, group, tk, tq, q_ranges, segs, seed, amp = prob
     hq = hkv * group
     g = torch.Generator().manual_seed(seed)
-    q = torch.randn(tq, hq, 128, generator=g).to(torch.bfloat16)
+    q = (amp * torch.randn(tq, hq, 128, generator=g)).to(torch.bfloat16)
     k = torch.randn(tk, hkv, 128, generator=g).to(torch.bfloat16)
     v = torch.randn(tk, hkv, 128, generator=g).to(torch.bfloat16)
     kr = np.array([iv for s in segs for iv in s], dtype=np.int32).reshape(-1, 2)
@@ -51,8 +54,11 @@ def test_random_rectangles_match_oracle(prob):
     assert mb.Context.get().status() == 0
     ref, ref_lse = O.range_attention(q.float(), k.float(), v.float(), qr, segs)
     rows = torch.cat([torch.arange(a, b) for a, b in q_ranges])
-    assert_close(out[rows.cuda()], ref[rows], what="tcgen05 vs oracle")
-    assert_close(twin[rows.cuda()], ref[rows], what="simt vs oracle")
+    # 2e-2 is the bound for outputs of unit scale; with amplified scores a row returns nearly a single V row, values
+    # reach 4-5, and one bf16 ulp there is already 0.031: the bound scales with the output magnitude above 2
+    tol = 2e-2 * max(1.0, float(ref[rows].abs().max()) / 2.0)
+    assert_close(out[rows.cuda()], ref[rows], max_abs=tol, what="tcgen05 vs oracle")
+    assert_close(twin[rows.cuda()], ref[rows], max_abs=tol, what="simt vs oracle")
     covered = torch.zeros(tq, dtype=torch.bool)
     covered[rows] = True
     assert (out.cpu()[~covered].float() == 5.0).all()          # rows of no range are never written
