@@ -139,8 +139,10 @@ MAGI_API int magi_kv_cache_append(magi_kv_cache* c, int layer, int chunk_id, con
 /* Frees the pages of a chunk in every layer (the reference never frees; its windows
  * - inference/pipeline/video_generate.py:467-508 - make old chunks dead). */
 MAGI_API int magi_kv_cache_evict(magi_kv_cache* c, int chunk_id);
-/* Copies a page back out as bf16 [n_tokens, Hkv, 128] (dequantising an FP8 page); for tests and for callers
- * that want the reference's materialised prefix (inference/model/dit/dit_module.py:914-915). */
+/* Copies a page back out as bf16 [n_tokens, Hkv, 128] (dequantising an FP8 page); for tests, for callers that want the
+ * reference's materialised prefix (inference/model/dit/dit_module.py:914-915), and - bf16 pages, k_out / v_out in pinned
+ * host memory - for spilling a page to the host tier (the reference's kv_offload, :803-811).  magi_kv_cache_append
+ * accepts pinned host sources the same way (the copy kernel reads them over PCIe), which brings a page back. */
 MAGI_API int magi_kv_cache_read(magi_kv_cache* c, int layer, int chunk_id, void* k_out, void* v_out, int n_tokens,
                        int token_offset, void* stream);
 /* Bytes of device memory the cache holds. */

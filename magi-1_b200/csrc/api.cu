@@ -262,8 +262,9 @@ extern "C" int magi_kv_cache_read(magi_kv_cache* c, int layer, int chunk_id, voi
   const int64_t row_elems = (int64_t)c->d.n_kv_heads * kHeadDim;
   const int64_t row0 = (int64_t)slot * c->page_cap + token_offset;
   const size_t bytes = (size_t)n_tokens * row_elems * 2;
-  MAGI_CUDA_OK(ctx, cudaMemcpyAsync(k_out, static_cast<uint16_t*>(c->k_pool) + row0 * row_elems, bytes, cudaMemcpyDeviceToDevice, st));
-  MAGI_CUDA_OK(ctx, cudaMemcpyAsync(v_out, static_cast<uint16_t*>(c->v_pool) + row0 * row_elems, bytes, cudaMemcpyDeviceToDevice, st));
+  // cudaMemcpyDefault: the destinations may be device memory or pinned host memory (the spill tier)
+  MAGI_CUDA_OK(ctx, cudaMemcpyAsync(k_out, static_cast<uint16_t*>(c->k_pool) + row0 * row_elems, bytes, cudaMemcpyDefault, st));
+  MAGI_CUDA_OK(ctx, cudaMemcpyAsync(v_out, static_cast<uint16_t*>(c->v_pool) + row0 * row_elems, bytes, cudaMemcpyDefault, st));
   return MAGI_OK;
 }
 

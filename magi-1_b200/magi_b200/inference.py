@@ -89,6 +89,46 @@ class InferenceParams:
         return self.cache
 
 
+class HostPageStore:
+    """Pinned-host tier under the page pool.
+
+    The reference's kv_offload keeps the whole per-layer cache in pinned host memory and copies the prefix to the GPU for
+    every layer of every step (inference/model/dit/dit_module.py:803-811, :915).  Here pages stay in HBM while a k window
+    can reach them; spill() moves the pages of one chunk (all layers) to pinned memory and frees its slots, prefetch()
+    brings them back on a side stream ahead of the step that needs them.  bf16 pages only (an fp8 page would be read
+    back dequantised)."""
+
+    def __init__(self, cache: ops.ChunkPagedKVCache):
+        if cache.dtype != "bf16":
+            raise ValueError("the host tier holds bf16 pages")
+        self.cache = cache
+        self.pages = {}  # chunk id -> (k [L, C, Hkv, 128], v) in pinned memory
+
+    def spill(self, chunk_id: int, stream=None) -> None:
+        """Stream-ordered on `stream` (default: the current stream, i.e. after the step that last used the page and
+        before anything that reuses its slot)."""
+        c = self.cache
+        shape = (c.n_layers, c.chunk_tokens, c.n_kv_heads, HEAD_DIM)
+        k = torch.empty(shape, dtype=torch.bfloat16).pin_memory()
+        v = torch.empty(shape, dtype=torch.bfloat16).pin_memory()
+        for layer in range(c.n_layers):
+            c.read_into(layer, chunk_id, k[layer], v[layer], stream)
+        c.evict(chunk_id)
+        self.pages[chunk_id] = (k, v)
+
+    def prefetch(self, chunk_id: int, stream: Optional[torch.cuda.Stream] = None) -> torch.cuda.Event:
+        """Bring a spilled chunk back into free slots on `stream` (a side stream overlaps it with compute); wait for the
+        returned event on the compute stream before the attention call that lists the chunk."""
+        k, v = self.pages.pop(chunk_id)
+        s = stream if stream is not None else torch.cuda.current_stream()
+        for layer in range(self.cache.n_layers):
+            self.cache.append_from_host(layer, chunk_id, k[layer], v[layer], s)
+        ev = torch.cuda.Event()
+        ev.record(s)
+        self._keep = (k, v)  # the pinned buffers must outlive the copies in flight
+        return ev
+
+
 class ProjInput:
     """The operand of the attention output projection, written in place by the two attention calls.
 

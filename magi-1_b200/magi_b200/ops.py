@@ -198,6 +198,23 @@ class ChunkPagedKVCache:
     def evict(self, chunk_id: int):
         check(lib.magi_kv_cache_evict(self.handle, chunk_id), self.ctx.handle)
 
+    def read_into(self, layer: int, chunk_id: int, k_out: torch.Tensor, v_out: torch.Tensor, stream=None):
+        """Copy a whole page into caller-owned contiguous bf16 [chunk_tokens, Hkv, 128] tensors: device or pinned host."""
+        for t in (k_out, v_out):
+            if t.dtype != torch.bfloat16 or not t.is_contiguous() or tuple(t.shape) != (self.chunk_tokens, self.n_kv_heads, HEAD_DIM) \
+                    or not (t.is_cuda or t.is_pinned()):
+                raise ValueError("read_into needs contiguous bf16 [chunk_tokens, Hkv, 128] tensors on the device or in pinned memory")
+        check(lib.magi_kv_cache_read(self.handle, layer, chunk_id, k_out.data_ptr(), v_out.data_ptr(), self.chunk_tokens, 0,
+                                     _stream(stream)), self.ctx.handle)
+
+    def append_from_host(self, layer: int, chunk_id: int, k: torch.Tensor, v: torch.Tensor, stream=None):
+        """Fill a page from pinned host tensors [chunk_tokens, Hkv, 128] (read by the copy kernel over PCIe)."""
+        for t in (k, v):
+            if t.dtype != torch.bfloat16 or not t.is_contiguous() or not t.is_pinned() or t.shape[1] != self.n_kv_heads:
+                raise ValueError("append_from_host needs contiguous pinned bf16 [tokens, Hkv, 128] tensors")
+        check(lib.magi_kv_cache_append(self.handle, layer, chunk_id, k.data_ptr(), k.stride(0), k.stride(1),
+                                       v.data_ptr(), v.stride(0), v.stride(1), k.shape[0], 0, _stream(stream)), self.ctx.handle)
+
     def read(self, layer: int, chunk_id: int, n_tokens: Optional[int] = None, token_offset: int = 0, stream=None):
         n = self.chunk_tokens - token_offset if n_tokens is None else n_tokens
         dev = torch.device("cuda", self.ctx.device)

@@ -117,3 +117,47 @@ def test_long_clip_streams_through_a_small_page_pool():
     assert ip.first_live_chunk == n_chunks + 1 - window[0]
     assert ip.cache.max_chunks == 9
     ip.cache.close()
+
+
+def test_host_tier_spill_and_prefetch_round_trip():
+    """Pages spilled to pinned host memory and prefetched back on a side stream give bit-identical attention."""
+    import magi_b200 as mb
+    from magi_b200 import host
+    from magi_b200.inference import HostPageStore
+    Cc, n_layers = 200, 2
+    g = torch.Generator().manual_seed(63)
+    cache = mb.ChunkPagedKVCache(n_layers=n_layers, max_chunks=3, chunk_tokens=Cc, n_kv_heads=HKV)
+    pages = {}
+    for c in range(3):
+        for layer in range(n_layers):
+            k = torch.randn(Cc, HKV, 128, generator=g).to(torch.bfloat16).cuda()
+            v = torch.randn(Cc, HKV, 128, generator=g).to(torch.bfloat16).cuda()
+            cache.append(layer, c, k, v)
+            pages[(layer, c)] = (k, v)
+    q = torch.randn(Cc, HQ, 128, generator=g).to(torch.bfloat16).cuda()
+    kc = torch.randn(Cc, HKV, 128, generator=g).to(torch.bfloat16).cuda()
+    vc = torch.randn(Cc, HKV, 128, generator=g).to(torch.bfloat16).cuda()
+    qr = np.array([[0, Cc]], dtype=np.int32)
+    kr = np.array([[0, 4 * Cc]], dtype=np.int32)
+    before = [mb.chunk_attn(q, kc, vc, qr, kr, Cc, 4 * Cc, cache=cache, layer=l, prefix_chunk_ids=[0, 1, 2])[0].clone()
+              for l in range(n_layers)]
+    tier = HostPageStore(cache)
+    tier.spill(0)                                              # frees a slot in every layer
+    with pytest.raises(mb.MagiError):
+        mb.chunk_attn(q, kc, vc, qr, kr, Cc, 4 * Cc, cache=cache, layer=0, prefix_chunk_ids=[0, 1, 2])
+    for layer in range(n_layers):                              # the freed slot takes a new chunk
+        cache.append(layer, 3, kc, vc)
+    cache.evict(3)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    ev = tier.prefetch(0, side)                                # back from the host while the main stream is free to compute
+    torch.cuda.current_stream().wait_event(ev)
+    after = [mb.chunk_attn(q, kc, vc, qr, kr, Cc, 4 * Cc, cache=cache, layer=l, prefix_chunk_ids=[0, 1, 2])[0]
+             for l in range(n_layers)]
+    torch.cuda.synchronize()
+    for a, b in zip(before, after):
+        assert torch.equal(a, b)
+    for layer in range(n_layers):
+        k_page, v_page = cache.read(layer, 0)
+        assert torch.equal(k_page, pages[(layer, 0)][0]) and torch.equal(v_page, pages[(layer, 0)][1])
+    cache.close()
