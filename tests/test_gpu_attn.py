@@ -170,6 +170,32 @@ def test_large_magnitude_scores_stay_finite(mb):
     assert torch.allclose(lse.cpu(), ref_lse, atol=5e-2, rtol=1e-3)
 
 
+@pytest.mark.parametrize("n_seq", [257, 1024])
+def test_varlen_batch_of_many_ranges(mb, n_seq):
+    """Hundreds of short sequences in one call (cu_seqlens style): the planner works one thread per range - prefix sums
+    for the segment and work-item lists, a rank sort for longest-K-first - and must agree with the per-range oracle,
+    empty key ranges included."""
+    rng = np.random.default_rng(n_seq)
+    lq = rng.integers(1, 90, size=n_seq)
+    lk = rng.integers(0, 200, size=n_seq)
+    lk[rng.integers(0, n_seq, size=n_seq // 16)] = 0           # some sequences have no keys at all
+    cq = np.concatenate([[0], np.cumsum(lq)])
+    ck = np.concatenate([[0], np.cumsum(lk)])
+    qr = np.stack([cq[:-1], cq[1:]], 1).astype(np.int32)
+    kr = np.stack([ck[:-1], ck[1:]], 1).astype(np.int32)
+    g = torch.Generator().manual_seed(n_seq)
+    q = torch.randn(int(cq[-1]), 4, 128, generator=g)
+    k = torch.randn(int(ck[-1]), 2, 128, generator=g)
+    v = torch.randn(int(ck[-1]), 2, 128, generator=g)
+    out, lse, (qb, kb, vb) = _run(mb, q, k, v, qr, kr, int(lq.max()))
+    ref, ref_lse = O.range_attention(qb, kb, vb, qr, as_segments(kr))
+    assert_close(out, ref, what=f"{n_seq} ranges")
+    live = torch.cat([torch.arange(a, b) for (a, b), n in zip(qr, lk) if n > 0])
+    assert torch.allclose(lse.cpu()[live], ref_lse[live], atol=3e-3, rtol=1e-3)
+    dead = torch.cat([torch.arange(a, b) for (a, b), n in zip(qr, lk) if n == 0])
+    assert (out.cpu()[dead].float() == 0).all() and torch.isinf(lse.cpu()[dead]).all()
+
+
 @pytest.mark.parametrize("step", [0.5, 2.0, 9.0, 40.0])
 def test_reference_maximum_keeps_growing_tile_after_tile(mb, step):
     """Keys whose scores climb by about `step` (in log2 units of the softmax weights) from one 128-token tile to the
