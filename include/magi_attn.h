@@ -52,7 +52,7 @@ MAGI_API int magi_version(void);
 MAGI_API const char* magi_strerror(int code);
 
 /* One context per GPU worker; mirrors "one Python process per GPU" of the reference launcher
- * (example/24B/run.sh:27-38).  Allocates the plan workspace (1 MiB) on `device`.  Fails with MAGI_E_ARCH on
+ * (example/24B/run.sh:27-38).  Allocates the plan workspace (640 KiB) on `device`.  Fails with MAGI_E_ARCH on
  * anything but sm_100. */
 MAGI_API int magi_ctx_create(int device, magi_ctx** out);
 MAGI_API int magi_ctx_destroy(magi_ctx* ctx);
@@ -187,7 +187,10 @@ typedef struct {
   int32_t layer;
   int32_t n_prefix_chunks;       /* P <= 64                                                              */
   const int32_t* prefix_chunk_ids; /* HOST int32 [P]                                                     */
-  /* FP8 only: fp32 scales [n_blocks, heads]; 128-token blocks counted from each multiple of scale_chunk_tokens */
+  /* FP8 only: fp32 scales [n_blocks, heads]; 128-token blocks counted from each multiple of scale_chunk_tokens, so
+   * q_scale has ceil(total_q / scale_chunk_tokens) * ceil(scale_chunk_tokens / 128) rows of n_q_heads entries, k_scale
+   * and v_scale the same with total_k and n_kv_heads (what magi_quantize_e4m3_block128 writes); prefix pages carry
+   * their own scales inside the cache.  A block without tokens is never read. */
   const float* q_scale;
   const float* k_scale;
   const float* v_scale;
@@ -201,7 +204,9 @@ typedef struct {
    * "(cp sq) hn hd -> sq (cp hn) hd" re-layout at :596, fused into the attention epilogue): q row t belongs to the
    * context-parallel rank d with o_peer_offsets[d] <= t < o_peer_offsets[d+1] and is stored at
    * o_peer_ptrs[d] + (t - o_peer_offsets[d]) * o_stride_t + (o_head_offset + head) * o_stride_h, with plain stores
-   * (peer-mapped pointers from magi_peer_open for d != own rank).  `out` is then ignored.  HOST arrays, n_o_peers <= 16. */
+   * (peer-mapped pointers from magi_peer_open for d != own rank).  `out` is then ignored.  HOST arrays, n_o_peers <= 16.
+   * Both the bf16 and the FP8 kernel support it; lse must be NULL; rows of a q-range without keys are stored as zeros at
+   * the same destinations. */
   void* const* o_peer_ptrs;
   const int32_t* o_peer_offsets;   /* [n_o_peers + 1] */
   int32_t n_o_peers;
@@ -216,8 +221,10 @@ typedef struct {
   int64_t o_stride_block;
 } magi_attn_params;
 MAGI_API int magi_chunk_attn_fwd(magi_ctx* ctx, const magi_attn_params* p, void* stream);
-/* Diagnostic twin: same plan, same arguments (bf16 only), plain CUDA-core arithmetic in fp32.  It exists so a
- * numerical failure can be attributed to the plan or to the tensor-core kernel; it is not a dispatch target. */
+/* DIAGNOSTIC ONLY - not a fallback and never dispatched to by the library or its Python shim: same plan, same arguments
+ * (bf16 only, no fused output exchange), plain CUDA-core arithmetic in fp32, one to two orders of magnitude slower.  It
+ * exists so that a numerical failure can be attributed to the plan or to the tensor-core kernel.  No reference
+ * counterpart. */
 MAGI_API int magi_chunk_attn_fwd_simt(magi_ctx* ctx, const magi_attn_params* p, void* stream);
 
 /* Attention forward for callers that are not allowed to allocate device memory.  It has no counterpart in the
@@ -235,7 +242,10 @@ MAGI_API int magi_chunk_attn_fwd_simt(magi_ctx* ctx, const magi_attn_params* p, 
  *     clears the part that must start at zero.  Two calls whose GPU work can overlap (different streams, or several
  *     threads) race on it: keep the calls of one device stream-ordered.
  *   - status_dev (device int32*, may be NULL) receives, stream-ordered, the planner/kernel status word
- *     (0, MAGI_E_RANGE or MAGI_E_TIMEOUT).  err/err_len (host buffer, may be NULL/0) receives the failure text. */
+ *     (0, MAGI_E_RANGE or MAGI_E_TIMEOUT) of THIS call.  Clearing the scratch header at the start of every call also
+ *     clears that word, so a failure of an earlier call (a sticky MAGI_E_TIMEOUT included) is visible only to the
+ *     caller that passed status_dev on that earlier call; without status_dev a device-side failure goes unreported.
+ *     err/err_len (host buffer, may be NULL/0) receives the failure text. */
 MAGI_API int magi_chunk_attn_fwd_noalloc(const magi_attn_params* p, void* stream, int32_t* status_dev, char* err,
                                          int err_len);
 

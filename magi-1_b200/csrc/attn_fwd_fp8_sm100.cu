@@ -14,6 +14,7 @@
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
+#include "attn_epilogue.cuh"
 
 namespace magi {
 using namespace ptx;
@@ -39,6 +40,11 @@ struct Attn8Params {
   const float* q_scale;     // [q blocks, Hq]
   const float* k_scale[2];  // [0] current [blocks, Hkv], [1] cache pool
   const float* v_scale[2];
+  // fused output exchange, as in the bf16 kernel: see out_row()
+  int n_peers;
+  int head_offset;
+  int peer_off[17];
+  __nv_bfloat16* peer_out[16];
 };
 
 template <bool kTwoTerm>
@@ -75,14 +81,8 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int n_tiles = it.n_tiles;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  if (n_tiles == 0) {
-    for (int idx = threadIdx.x; idx < it.q_rows * (kHeadDim / 8); idx += blockDim.x) {
-      const int r = idx / (kHeadDim / 8), c = idx % (kHeadDim / 8);
-      *reinterpret_cast<uint4*>(p.out + (int64_t)(it.q_row0 + r) * p.o_stride_t + head_col(p, head) + c * 8) =
-          make_uint4(0, 0, 0, 0);
-    }
-    if (p.lse)
-      for (int r = threadIdx.x; r < it.q_rows; r += blockDim.x) p.lse[(int64_t)(it.q_row0 + r) * p.n_q_heads + head] = -INFINITY;
+  if (n_tiles == 0) {  // a q-range with no keys: zeros (lse = -inf), stored wherever the rows live (local or peer)
+    zero_fill_item(p, it, head);
     return;
   }
 
@@ -214,7 +214,9 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + x * kTileN;
     const uint32_t tO = tmem_base + lane_base + 2 * kTileN + x * kHeadDim;
-    const float sq = p.q_scale[(int64_t)(it.q_blk0 + x) * p.n_q_heads + head] * p.scale_log2;
+    // the second Q tile of a work item with at most 128 rows has no scale block of its own (for the last item of the last
+    // chunk the index would be one row past the scale tensor): its rows are never stored, any finite scale will do
+    const float sq = (x * kTileM < it.q_rows ? __ldg(p.q_scale + (int64_t)(it.q_blk0 + x) * p.n_q_heads + head) : 1.0f) * p.scale_log2;
     float m_used = -INFINITY;  // running reference maximum of s' = S*sq*sk*scale*log2e + log2(sv)
     float l = 0.f;             // sum_j rowsum(16 w_j) / sv_j
     int j = 0;
@@ -315,24 +317,13 @@ attn_fwd_fp8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const int r_in_item = x * kTileM + row;
       const bool valid_row = r_in_item < it.q_rows;
       const float inv = 1.0f / l;
-      __nv_bfloat16* dst = p.out + (int64_t)(it.q_row0 + r_in_item) * p.o_stride_t + head_col(p, head);
-#pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t o[32];
-        tmem_ld32(tO + c4 * 32, o);
-        tmem_wait_ld();
-        if (valid_row) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(o[8 * c + 0]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
-            v.y = pack_bf16x2(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
-            v.z = pack_bf16x2(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
-            v.w = pack_bf16x2(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c4 * 32 + c * 8) = v;
-          }
-        }
-      }
+      // Staging memory for the row-wise stores: every K/V stage except the one holding the last V tile is idle by now
+      // (o_full[x] follows, in the issuing thread's order, every UMMA that read an earlier stage, and the producer has
+      // nothing left to load), so each of the eight softmax warps takes half a stage (8 KB) after that one.
+      const int last_v_stage = (2 * n_tiles - 1) % kStages8;
+      const int w8 = x * 4 + quarter;
+      uint8_t* stage = ring + ((last_v_stage + 1 + (w8 >> 1)) % kStages8) * kTile8 + (w8 & 1) * 8192;
+      store_o_rows_staged(p, it, head, x, quarter, lane, tO, inv, stage);
       if (p.lse && valid_row)
         p.lse[(int64_t)(it.q_row0 + r_in_item) * p.n_q_heads + head] = (m_used + log2f(l) - kPScaleLog2) * 0.6931471805599453f;
     }
@@ -397,6 +388,7 @@ int launch_attn_fp8(magi_ctx* ctx, const magi_attn_params* p, int max_items, cud
   kp.k_scale[1] = has_cache ? p->cache->k_scale : p->k_scale;
   kp.v_scale[1] = has_cache ? p->cache->v_scale : p->v_scale;
   if (!has_new) { kp.k_scale[0] = kp.k_scale[1]; kp.v_scale[0] = kp.v_scale[1]; }
+  fill_peer_table(kp, p);
   const dim3 grid(max_items, p->n_q_heads);
   if (p->q_lo)
     attn_fwd_fp8_kernel<true><<<grid, kThreads8, Smem8<true>::kDynamic, stream>>>(tq, tql, tk, tv, tkc, tvc, kp);

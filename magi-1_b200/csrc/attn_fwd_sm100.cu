@@ -18,6 +18,7 @@
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
+#include "attn_epilogue.cuh"
 
 namespace magi {
 using namespace ptx;
@@ -45,28 +46,6 @@ struct AttnKernelParams {
   int peer_off[17];
   __nv_bfloat16* peer_out[16];
 };
-
-// Optional device-side timeline (compiled only with -DMAGI_TRACE, never in the shipped library): CTA (0,0) stamps
-// clock64() at the hand-off points of its first kTraceIters K/V tiles.
-#ifdef MAGI_TRACE
-#ifndef MAGI_TRACE_J0
-#define MAGI_TRACE_J0 0
-#endif
-#ifndef MAGI_TRACE_HEAD
-#define MAGI_TRACE_HEAD 0
-#endif
-constexpr int kTraceIters = 24;
-constexpr int kTraceEvents = 8;
-__device__ long long g_trace[4][kTraceIters][kTraceEvents];  // [0] UMMA issuer, [1] softmax WG0, [2] softmax WG1, [3] producer (per fill)
-__device__ long long g_cta_log[8192][4];  // per CTA: globaltimer start, end, n_tiles, smid
-#define MAGI_STAMP(role, j, ev)                                                         \
-  do {                                                                                  \
-    if (blockIdx.x == 0 && blockIdx.y == MAGI_TRACE_HEAD && (j) >= MAGI_TRACE_J0 && (j) < MAGI_TRACE_J0 + kTraceIters) \
-      g_trace[role][(j) - MAGI_TRACE_J0][ev] = clock64();                                                            \
-  } while (0)
-#else
-#define MAGI_STAMP(role, j, ev) do { } while (0)
-#endif
 
 // Shared memory: Q (2 tiles, 64 KB) + a ring of 5 K/V stages (160 KB): K_j and V_j alternate through the ring, so the
 // producer runs 2.5 K/V tile pairs ahead of the UMMAs.  (With 4 stages the TMA round trip was exposed: ~1000 of the
@@ -112,19 +91,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-#ifdef MAGI_TRACE
-  long long cta_t0 = 0;
-  if (threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(cta_t0));
-#endif
-  if (n_tiles == 0) {  // a q-range with no keys: define the output as zeros, lse = -inf
-    for (int idx = threadIdx.x; idx < it.q_rows * (kHeadDim / 8); idx += blockDim.x) {
-      const int r = idx / (kHeadDim / 8), c = idx % (kHeadDim / 8);
-      *reinterpret_cast<uint4*>(p.out + (int64_t)(it.q_row0 + r) * p.o_stride_t + head_col(p, head) + c * 8) =
-          make_uint4(0, 0, 0, 0);
-    }
-    if (p.lse)
-      for (int r = threadIdx.x; r < it.q_rows; r += blockDim.x)
-        p.lse[(int64_t)(it.q_row0 + r) * p.n_q_heads + head] = -INFINITY;
+  if (n_tiles == 0) {  // a q-range with no keys: zeros (lse = -inf), stored wherever the rows live (local or peer)
+    zero_fill_item(p, it, head);
     return;
   }
 
@@ -184,10 +152,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int kv = 0; kv < 2; ++kv, ++fill) {
             const int stage = fill % kStages;
             const int use = fill / kStages;
-            MAGI_STAMP(3, fill, 0);
             if (use > 0) ok = mbar_wait(&kv_empty[stage], (use & 1) ^ 1, abort_flag);
             if (!ok) break;
-            MAGI_STAMP(3, fill, 1);
             mbar_expect_tx(&kv_full[stage], kTileBytes);
             const CUtensorMap* m = kv ? mv : mk;
             tma_load_3d(ring + stage * kTileBytes, m, &kv_full[stage], 0, kv_head, sg.row0 + t0);
@@ -257,10 +223,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (!ok) break;
-          MAGI_STAMP(0, j, 4 * x + 0);
           ok = mbar_wait(&p_full[x], j & 1, abort_flag);
           if (!ok) break;
-          MAGI_STAMP(0, j, 4 * x + 1);
           tc_fence_after_sync();
           issue_pv(x, v_stage, j == 0);
           if (!more) umma_commit(&o_full[x]);  // only the epilogue waits for O (a later S_x implies the earlier PV_x)
@@ -270,7 +234,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             umma_commit(&s_full[x]);
             if (x == 1) umma_commit(&kv_empty[k_stage]);
           }
-          MAGI_STAMP(0, j, 4 * x + 2);
         }
       }
     }
@@ -292,10 +255,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const Segment sg = pv.segs[sg_i];
       for (int t0 = 0; t0 < sg.len && ok; t0 += kTileN, ++j) {
         const int valid = min(kTileN, sg.len - t0);
-        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 0);
         ok = mbar_wait(&s_full[x], j & 1, abort_flag);
         if (!ok) break;
-        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 1);
         tc_fence_after_sync();
         // S_x(j) complete implies PV_x(j-1) complete (same issuing thread, in order), so O_x may be rescaled here.
         uint32_t s[kTileN];
@@ -312,7 +273,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         };
         load_s();
-        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 2);
         float alpha = 1.0f, rowsum = 0.f;
         bool redo = (j == 0);
         if (j > 0) {
@@ -343,7 +303,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           redo = __any_sync(0xffffffffu, !(rowsum <= kRedoRowSum));
           if (redo) load_s();
         }
-        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 3);
         if (redo) {
           // Exact path (first tile, or the running maximum moved): new reference maximum, then the exponentials.
           float mxa[8];
@@ -375,7 +334,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           rowsum = (rs[0] + rs[2]) + (rs[1] + rs[3]);
           m_used = m_cur;
         }
-        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 4);
         tmem_st32(tS, s);
         tmem_st32(tS + 32, s + 32);
         if (redo && j > 0) {
@@ -390,12 +348,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
         l = l * alpha + rowsum;
-        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 5);
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[x]);
-        if (quarter == 0 && lane == 0) MAGI_STAMP(1 + x, j, 6);
       }
     }
     if (ok) ok = mbar_wait(&o_full[x], 0, abort_flag);
@@ -404,46 +360,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int r_in_item = x * kTileM + row;
       const bool valid_row = r_in_item < it.q_rows;
       const float inv = 1.0f / l;
-      // Stage the warp's 32 rows x 256 B through the (now idle) shared memory of its own Q tile, so that the global
-      // stores are whole 256-byte rows per half-warp instead of 16-byte pieces of 32 different rows; this matters when
-      // the destination is a peer GPU (NVLink packets) and costs nothing locally.  16-byte chunks are XOR-swizzled
-      // by the row index: conflict-free in both directions.
-      uint8_t* stage = sQ + x * kTileBytes + quarter * (32 * 256);
-#pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t o[32];
-        tmem_ld32(tO + c4 * 32, o);
-        tmem_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint4 v;
-          v.x = pack_bf16x2(__uint_as_float(o[8 * c + 0]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
-          v.y = pack_bf16x2(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
-          v.z = pack_bf16x2(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
-          v.w = pack_bf16x2(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
-          *reinterpret_cast<uint4*>(stage + lane * 256 + (((c4 * 4 + c) ^ (lane & 15)) << 4)) = v;
-        }
-      }
-      __syncwarp();
-      const int l16 = lane & 15, hsel = lane >> 4;
-#pragma unroll 4
-      for (int i = 0; i < 16; ++i) {
-        const int rr = 2 * i + hsel;                       // row inside this warp's 32
-        const int r_item = x * kTileM + quarter * 32 + rr;  // row inside the work item
-        if (r_item < it.q_rows) {
-          const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 256 + (l16 << 4));
-          const int t = it.q_row0 + r_item;
-          __nv_bfloat16* dst_row;
-          if (p.n_peers > 0) {  // the row goes to the rank that owns this token, at this rank's global head position
-            int d = 0;
-            while (d + 1 < p.n_peers && t >= p.peer_off[d + 1]) ++d;
-            dst_row = p.peer_out[d] + (int64_t)(t - p.peer_off[d]) * p.o_stride_t + head_col(p, p.head_offset + head);
-          } else {
-            dst_row = p.out + (int64_t)t * p.o_stride_t + head_col(p, head);
-          }
-          *reinterpret_cast<uint4*>(dst_row + ((l16 ^ (rr & 15)) << 3)) = v;
-        }
-      }
+      // the warp's 32 rows go through the (now idle) shared memory of its own Q tile: see store_o_rows_staged
+      store_o_rows_staged(p, it, head, x, quarter, lane, tO, inv, sQ + x * kTileBytes + quarter * (32 * 256));
       if (p.lse && valid_row)
         p.lse[(int64_t)(it.q_row0 + r_in_item) * p.n_q_heads + head] = m_used * p.scale + logf(l);
     }
@@ -457,21 +375,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
-#ifdef MAGI_TRACE
-  if (threadIdx.x == 0) {
-    long long t1;
-    unsigned smid;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
-    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-    const int id = blockIdx.y * gridDim.x + blockIdx.x;
-    if (id < 8192) {
-      g_cta_log[id][0] = cta_t0;
-      g_cta_log[id][1] = t1;
-      g_cta_log[id][2] = n_tiles;
-      g_cta_log[id][3] = smid;
-    }
-  }
-#endif
 }
 
 // ---------------------------------------------------------------------------------------------- host side
@@ -509,17 +412,8 @@ int make_tile_map(magi_ctx* ctx, CUtensorMap* m, const void* base, int64_t strid
   return MAGI_OK;
 }
 
-// Opt in to > 48 KB of dynamic shared memory; called once per context with its device current.
-#ifdef MAGI_TRACE
-extern "C" __attribute__((visibility("default"))) int magi_debug_read_cta_log(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_cta_log, sizeof(g_cta_log));
-}
-extern "C" __attribute__((visibility("default"))) int magi_debug_read_trace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(g_trace));
-}
-#endif
-
 int attn_fp8_init_device(magi_ctx* ctx);
+// Opt in to > 48 KB of dynamic shared memory; called once per context with its device current.
 int attn_init_device(magi_ctx* ctx) {
   if (int rc = attn_fp8_init_device(ctx)) return rc;
   MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::kDynamic));
@@ -559,10 +453,7 @@ int launch_attn_bf16(magi_ctx* ctx, const magi_attn_params* p, int max_items, cu
   kp.group = p->n_q_heads / p->n_kv_heads;
   kp.scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / sqrtf((float)kHeadDim);
   kp.scale_log2 = kp.scale * 1.4426950408889634f;
-  kp.n_peers = p->n_o_peers;
-  kp.head_offset = p->o_head_offset;
-  for (int i = 0; i < 17; ++i) kp.peer_off[i] = i <= p->n_o_peers && p->n_o_peers > 0 ? p->o_peer_offsets[i] : 0;
-  for (int i = 0; i < 16; ++i) kp.peer_out[i] = i < p->n_o_peers ? reinterpret_cast<__nv_bfloat16*>(p->o_peer_ptrs[i]) : nullptr;
+  fill_peer_table(kp, p);
 
   dim3 grid(max_items, p->n_q_heads, 1);
   attn_fwd_kernel<<<grid, kAttnThreads, SmemLayout::kDynamic, stream>>>(tq, tk, tv, tkc, tvc, kp);

@@ -1,7 +1,9 @@
 // Internal declarations shared by the translation units of libmagi_attn.so.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 #include <stdio.h>
 
@@ -84,6 +86,42 @@ template <class P>
 __device__ __forceinline__ int64_t head_col(const P& p, int h) {
   return p.o_hpb > 0 ? (int64_t)(h / p.o_hpb) * p.o_stride_block + (int64_t)(h % p.o_hpb) * p.o_stride_h
                      : (int64_t)h * p.o_stride_h;
+}
+
+// Where the 128 output columns of q row `t`, (local) head `h` go.  Plain output: out + t * o_stride_t + head_col(h).
+// Fused output exchange (n_peers > 0): the row belongs to the rank d with peer_off[d] <= t < peer_off[d+1] and lands in
+// that rank's result buffer at this rank's global head position.  P carries out, o_stride_*, o_hpb, n_peers, head_offset,
+// peer_off[17], peer_out[16].
+template <class P>
+__device__ __forceinline__ __nv_bfloat16* out_row(const P& p, int t, int h) {
+  if (p.n_peers > 0) {
+    int d = 0;
+    while (d + 1 < p.n_peers && t >= p.peer_off[d + 1]) ++d;
+    return p.peer_out[d] + (int64_t)(t - p.peer_off[d]) * p.o_stride_t + head_col(p, p.head_offset + h);
+  }
+  return p.out + (int64_t)t * p.o_stride_t + head_col(p, h);
+}
+
+// A q-range without keys: the output rows are defined as zeros (lse = -inf), wherever they live.
+template <class P>
+__device__ __forceinline__ void zero_fill_item(const P& p, const WorkItem& it, int head) {
+  for (int idx = threadIdx.x; idx < it.q_rows * (kHeadDim / 8); idx += blockDim.x) {
+    const int r = idx / (kHeadDim / 8), c = idx % (kHeadDim / 8);
+    *reinterpret_cast<uint4*>(out_row(p, it.q_row0 + r, head) + c * 8) = make_uint4(0, 0, 0, 0);
+  }
+  if (p.lse)
+    for (int r = threadIdx.x; r < it.q_rows; r += blockDim.x)
+      p.lse[(int64_t)(it.q_row0 + r) * p.n_q_heads + head] = -INFINITY;
+}
+
+// Host: copies the peer table of the call into the by-value kernel parameters.
+template <class P>
+inline void fill_peer_table(P& kp, const magi_attn_params* p) {
+  kp.n_peers = p->n_o_peers;
+  kp.head_offset = p->o_head_offset;
+  for (int i = 0; i < 17; ++i) kp.peer_off[i] = (p->n_o_peers > 0 && i <= p->n_o_peers) ? p->o_peer_offsets[i] : 0;
+  for (int i = 0; i < 16; ++i)
+    kp.peer_out[i] = i < p->n_o_peers ? reinterpret_cast<__nv_bfloat16*>(p->o_peer_ptrs[i]) : nullptr;
 }
 
 }  // namespace magi

@@ -3,15 +3,16 @@
 // fp32 upcast, LayerNorm over the 128 channels with weight gamma+1 and bias (:355-357), non-interleaved
 // rotary on the first 2*rot_pairs channels in fp32, one rounding to bf16 at the end.
 //
-// Main kernel (rot_pairs a multiple of 8): a HALF-warp owns one (token, head) row: lane l of 16 holds channels 8l..8l+7
-// (16-byte loads and stores, 256 contiguous bytes per half-warp), so a warp instruction serves two rows; row index
-// arithmetic is 32-bit.  Rotary partners (c, c+rot_pairs) sit rot_pairs/8 lanes apart and are exchanged by shuffles.
-// The generic kernel (4 channels per lane, one row per warp) covers the remaining rot_pairs and the plain strided copy.
+// Main kernel (prologue16_kernel): a HALF-warp owns one (token, head) row, 8 channels per lane with both channels of a
+// rotary pair in the same lane, so a warp instruction serves two rows and the rotation needs no shuffle; row index
+// arithmetic is 32-bit.  The generic kernel (4 channels per lane, one row per warp) covers source-blocked inputs,
+// rows that are only 8-byte aligned and the plain strided copy.
 #include <cuda_bf16.h>
 
 #include <initializer_list>
 
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace magi {
 
@@ -127,43 +128,40 @@ __global__ void __launch_bounds__(256) prologue_kernel(PrologueKernelParams p) {
   }
 }
 
-__device__ __forceinline__ float half_warp_sum(float v) {
-#pragma unroll
-  for (int off = 8; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-  return v;
-}
-
 constexpr int kRows16PerIter = 4;  // rows (heads) per half-warp in flight: 1 KB of loads per half-warp
 
+// Main kernel.  A half-warp owns one (token, head) row of 128 channels, 8 per lane, laid out so that a rotary pair
+// (c, c + rot_pairs) lives in ONE thread: lane l < rot_pairs/4 holds channels 4l..4l+3 and rot_pairs+4l..rot_pairs+4l+3,
+// the remaining lanes hold the 128 - 2*rot_pairs pass-through channels, 8 consecutive ones each.  Every lane therefore
+// moves two 8-byte pieces of the 256-byte row, the rotation needs no shuffle and each lane loads only its 4 cos / 4 sin.
+// The statistics are taken in one pass (sum and sum of squares, two independent 4-level butterflies; var = E[x^2] - mean^2
+// in fp32, far inside the bf16 rounding of the result), and the normalisation runs as packed fp32 pairs.
 // Work unit of a half-warp: one token x `hg` consecutive heads (hg divides H).  cos/sin of the token are loaded once per
 // unit and reused for its heads; the heads of a token are contiguous rows, so a unit streams hg * 256 contiguous bytes.
-__global__ void __launch_bounds__(256, 4) prologue16_kernel(PrologueKernelParams p, int hg) {
+__global__ void __launch_bounds__(256, 3) prologue16_kernel(PrologueKernelParams p, int hg) {
+  using namespace ptx;
   const int lane = threadIdx.x & 31;
   const int l16 = lane & 15;
   const unsigned hw_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;  // half-warp id
   const unsigned n_hw = (gridDim.x * blockDim.x) >> 4;
   const unsigned groups = (unsigned)p.H / (unsigned)hg;
   const unsigned n_units = (unsigned)p.T * groups;
-  const int d = l16 * 8;
+  const int rp4 = p.rot_pairs >> 2;
+  const bool rot = l16 < rp4;
+  const int c0 = rot ? 4 * l16 : 2 * p.rot_pairs + 8 * (l16 - rp4);  // first four channels of this lane
+  const int c1 = rot ? p.rot_pairs + 4 * l16 : c0 + 4;               // second four (the rotary partners)
 
-  float g[8], b[8];
+  uint64_t g2[4], b2[4];  // (gamma + 1, beta) as packed pairs: [0],[1] = channels c0.., [2],[3] = channels c1..
   {
-    const float4 g0 = *reinterpret_cast<const float4*>(p.gamma + d), g1 = *reinterpret_cast<const float4*>(p.gamma + d + 4);
-    g[0] = g0.x + 1.f; g[1] = g0.y + 1.f; g[2] = g0.z + 1.f; g[3] = g0.w + 1.f;
-    g[4] = g1.x + 1.f; g[5] = g1.y + 1.f; g[6] = g1.z + 1.f; g[7] = g1.w + 1.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) b[i] = 0.f;
+    const float4 ga = *reinterpret_cast<const float4*>(p.gamma + c0), gb = *reinterpret_cast<const float4*>(p.gamma + c1);
+    g2[0] = f2_pack(ga.x + 1.f, ga.y + 1.f); g2[1] = f2_pack(ga.z + 1.f, ga.w + 1.f);
+    g2[2] = f2_pack(gb.x + 1.f, gb.y + 1.f); g2[3] = f2_pack(gb.z + 1.f, gb.w + 1.f);
+    b2[0] = b2[1] = b2[2] = b2[3] = f2_pack(0.f, 0.f);
     if (p.beta && p.norm_mode == MAGI_NORM_LAYERNORM_1P) {
-      const float4 b0 = *reinterpret_cast<const float4*>(p.beta + d), b1 = *reinterpret_cast<const float4*>(p.beta + d + 4);
-      b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+      const float4 ba = *reinterpret_cast<const float4*>(p.beta + c0), bb = *reinterpret_cast<const float4*>(p.beta + c1);
+      b2[0] = f2_pack(ba.x, ba.y); b2[1] = f2_pack(ba.z, ba.w); b2[2] = f2_pack(bb.x, bb.y); b2[3] = f2_pack(bb.z, bb.w);
     }
   }
-  const int rp8 = p.rot_pairs >> 3;
-  int partner = lane;
-  float sign = 0.f;
-  int cs_off = 0;
-  if (l16 < rp8) { partner = lane + rp8; sign = -1.f; cs_off = d; }
-  else if (l16 < 2 * rp8) { partner = lane - rp8; sign = 1.f; cs_off = d - p.rot_pairs; }
   const bool layernorm = p.norm_mode == MAGI_NORM_LAYERNORM_1P;
   const unsigned hpb = (unsigned)p.heads_per_block;
 
@@ -174,69 +172,62 @@ __global__ void __launch_bounds__(256, 4) prologue16_kernel(PrologueKernelParams
     const unsigned uc = unit_live ? unit : 0u;
     const unsigned t = uc / groups;
     const unsigned h0 = (uc - t * groups) * (unsigned)hg;
-    float c[8], sn[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) { c[k] = 1.f; sn[k] = 0.f; }
-    if (sign != 0.f) {
-      const float* cp = p.cos + (int64_t)t * p.rot_pairs + cs_off;
-      const float* sp = p.sin + (int64_t)t * p.rot_pairs + cs_off;
-      const float4 c0 = __ldg(reinterpret_cast<const float4*>(cp)), c1 = __ldg(reinterpret_cast<const float4*>(cp + 4));
-      const float4 s0 = __ldg(reinterpret_cast<const float4*>(sp)), s1 = __ldg(reinterpret_cast<const float4*>(sp + 4));
-      c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
-      sn[0] = sign * s0.x; sn[1] = sign * s0.y; sn[2] = sign * s0.z; sn[3] = sign * s0.w;
-      sn[4] = sign * s1.x; sn[5] = sign * s1.y; sn[6] = sign * s1.z; sn[7] = sign * s1.w;
+    float4 cs = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (rot) {
+      cs = __ldg(reinterpret_cast<const float4*>(p.cos + (int64_t)t * p.rot_pairs + 4 * l16));
+      sn = __ldg(reinterpret_cast<const float4*>(p.sin + (int64_t)t * p.rot_pairs + 4 * l16));
     }
-    const __nv_bfloat16* xrow = p.x + (int64_t)t * p.x_stride_t + d;
+    const __nv_bfloat16* xrow = p.x + (int64_t)t * p.x_stride_t;
     for (int hb = 0; hb < hg; hb += kRows16PerIter) {
-      uint4 raw[kRows16PerIter];
+      uint2 ra[kRows16PerIter], rb[kRows16PerIter];
 #pragma unroll
       for (int i = 0; i < kRows16PerIter; ++i) {
-        const unsigned h = h0 + min(hb + i, hg - 1);
-        raw[i] = __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)h * p.x_stride_h));
+        const __nv_bfloat16* xr = xrow + (int64_t)(h0 + min(hb + i, hg - 1)) * p.x_stride_h;
+        ra[i] = __ldg(reinterpret_cast<const uint2*>(xr + c0));
+        rb[i] = __ldg(reinterpret_cast<const uint2*>(xr + c1));
       }
 #pragma unroll
       for (int i = 0; i < kRows16PerIter; ++i) {
-        const __nv_bfloat162* pr = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
-        float v[8];
+        // bf16 -> fp32 is a 16-bit shift: (lo, hi) of each 32-bit word
+        const uint32_t w[4] = {ra[i].x, ra[i].y, rb[i].x, rb[i].y};
+        uint64_t v2[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) { v[2 * k] = __low2float(pr[k]); v[2 * k + 1] = __high2float(pr[k]); }
-        float y[8];
-        if (layernorm) {
-          const float mean = half_warp_sum(((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]))) * (1.f / kHeadDim);
-          float sq = 0.f;
+        for (int k = 0; k < 4; ++k) v2[k] = f2_pack(__uint_as_float(w[k] << 16), __uint_as_float(w[k] & 0xffff0000u));
+        uint64_t s2 = f2_add(f2_add(v2[0], v2[1]), f2_add(v2[2], v2[3]));
+        uint64_t q2 = f2_fma(v2[0], v2[0], f2_fma(v2[1], v2[1], f2_fma(v2[2], v2[2], f2_fma(v2[3], v2[3], f2_pack(0.f, 0.f)))));
+        float s_lo, s_hi, q_lo, q_hi;
+        f2_unpack(s2, s_lo, s_hi);
+        f2_unpack(q2, q_lo, q_hi);
+        float sum = s_lo + s_hi, sq = q_lo + q_hi;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) { v[k] -= mean; sq += v[k] * v[k]; }
-          const float rstd = rsqrtf(half_warp_sum(sq) * (1.f / kHeadDim) + p.eps);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) y[k] = v[k] * rstd * g[k] + b[k];
-        } else {
-          float sq = 0.f;
-#pragma unroll
-          for (int k = 0; k < 8; ++k) sq += v[k] * v[k];
-          const float rstd = rsqrtf(half_warp_sum(sq) * (1.f / kHeadDim) + p.eps);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) y[k] = v[k] * rstd * g[k];
+        for (int off = 8; off > 0; off >>= 1) {
+          sum += __shfl_xor_sync(0xffffffffu, sum, off);
+          sq += __shfl_xor_sync(0xffffffffu, sq, off);
         }
-        if (rp8 > 0) {  // uniform: every lane takes part in the exchange; lanes outside the rotary span keep y (c = 1, sn = 0)
+        const float mean = layernorm ? sum * (1.f / kHeadDim) : 0.f;
+        const float var = fmaxf(sq * (1.f / kHeadDim) - mean * mean, 0.f);
+        const float rstd = rsqrtf(var + p.eps);
+        const uint64_t r2 = f2_pack(rstd, rstd), m2 = f2_pack(-mean * rstd, -mean * rstd);
+        float y[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const float o = __shfl_sync(0xffffffffu, y[k], partner);
-            y[k] = y[k] * c[k] + o * sn[k];
+        for (int k = 0; k < 4; ++k) f2_unpack(f2_fma(f2_fma(v2[k], r2, m2), g2[k], b2[k]), y[2 * k], y[2 * k + 1]);
+        if (rot) {  // out1 = x1 cos - x2 sin, out2 = x1 sin + x2 cos  (x1 = y[0..3], x2 = y[4..7])
+          const float c[4] = {cs.x, cs.y, cs.z, cs.w}, s[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float x1 = y[k], x2 = y[4 + k];
+            y[k] = x1 * c[k] - x2 * s[k];
+            y[4 + k] = x2 * c[k] + x1 * s[k];
           }
         }
         if (unit_live && hb + i < hg) {
           const unsigned h = h0 + hb + i;
-          uint4 res;
-          __nv_bfloat162 t0 = __floats2bfloat162_rn(y[0], y[1]), t1 = __floats2bfloat162_rn(y[2], y[3]);
-          __nv_bfloat162 t2 = __floats2bfloat162_rn(y[4], y[5]), t3 = __floats2bfloat162_rn(y[6], y[7]);
-          res.x = *reinterpret_cast<const uint32_t*>(&t0);
-          res.y = *reinterpret_cast<const uint32_t*>(&t1);
-          res.z = *reinterpret_cast<const uint32_t*>(&t2);
-          res.w = *reinterpret_cast<const uint32_t*>(&t3);
           const unsigned blk = hpb > 0 ? h / hpb : 0u;
           const unsigned hs = hpb > 0 ? h - blk * hpb : h;
           __nv_bfloat16* ob = p.use_block_ptrs ? p.out_blocks[blk] : p.out + (int64_t)blk * p.out_stride_block;
-          *reinterpret_cast<uint4*>(ob + (int64_t)t * p.out_stride_t + (int64_t)hs * p.out_stride_h + d) = res;
+          __nv_bfloat16* orow = ob + (int64_t)t * p.out_stride_t + (int64_t)hs * p.out_stride_h;
+          *reinterpret_cast<uint2*>(orow + c0) = make_uint2(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]));
+          *reinterpret_cast<uint2*>(orow + c1) = make_uint2(pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
         }
       }
     }
@@ -305,8 +296,8 @@ static int launch_prologue(magi_ctx* ctx, const magi_prologue_params* p, bool no
   const int64_t want = (rows + 8 * kRowsPerIter - 1) / (8 * kRowsPerIter);
   const int64_t cap = (int64_t)ctx->sm_count * 8;  // 8 x 256 threads resident per SM
   const int blocks = (int)(want < cap ? want : cap);
-  // 16-byte path: needs rot_pairs % 8 == 0, no source blocking, 16-byte aligned rows on both sides, < 2^32 rows
-  const bool wide = norm_rope && (p->rot_pairs & 7) == 0 && k.x_heads_per_block == 0 && rows < (1ll << 32) &&
+  // half-warp path: no source blocking, 16-byte aligned rows on both sides, < 2^32 rows (rot_pairs % 4 == 0 was checked)
+  const bool wide = norm_rope && k.x_heads_per_block == 0 && rows < (1ll << 32) &&
                     !(reinterpret_cast<uintptr_t>(p->x) & 15) && !(reinterpret_cast<uintptr_t>(p->out) & 15) &&
                     !(p->x_stride_t & 7) && !(p->x_stride_h & 7) && !(p->out_stride_t & 7) && !(p->out_stride_h & 7) &&
                     !(p->out_stride_block & 7) && (p->rot_pairs == 0 || !((uintptr_t)p->cos & 15));

@@ -102,11 +102,18 @@ class HostPageStore:
         if cache.dtype != "bf16":
             raise ValueError("the host tier holds bf16 pages")
         self.cache = cache
-        self.pages = {}  # chunk id -> (k [L, C, Hkv, 128], v) in pinned memory
+        self.pages = {}      # chunk id -> (k [L, C, Hkv, 128], v) in pinned memory
+        self._inflight = {}  # chunk id -> (k, v, event): pinned buffers that copy kernels may still be reading
+
+    def _reap(self) -> None:
+        """Release the pinned buffers of prefetches whose copies have completed."""
+        for cid in [c for c, (_, _, ev) in self._inflight.items() if ev.query()]:
+            del self._inflight[cid]
 
     def spill(self, chunk_id: int, stream=None) -> None:
         """Stream-ordered on `stream` (default: the current stream, i.e. after the step that last used the page and
         before anything that reuses its slot)."""
+        self._reap()
         c = self.cache
         shape = (c.n_layers, c.chunk_tokens, c.n_kv_heads, HEAD_DIM)
         k = torch.empty(shape, dtype=torch.bfloat16).pin_memory()
@@ -119,13 +126,17 @@ class HostPageStore:
     def prefetch(self, chunk_id: int, stream: Optional[torch.cuda.Stream] = None) -> torch.cuda.Event:
         """Bring a spilled chunk back into free slots on `stream` (a side stream overlaps it with compute); wait for the
         returned event on the compute stream before the attention call that lists the chunk."""
+        self._reap()
         k, v = self.pages.pop(chunk_id)
         s = stream if stream is not None else torch.cuda.current_stream()
         for layer in range(self.cache.n_layers):
             self.cache.append_from_host(layer, chunk_id, k[layer], v[layer], s)
         ev = torch.cuda.Event()
         ev.record(s)
-        self._keep = (k, v)  # the pinned buffers must outlive the copies in flight
+        # The copy kernels read the pinned buffers over PCIe on `s`; torch's pinned-memory cache knows nothing about a
+        # library kernel, so the buffers are held here, per chunk, until the event has completed (several prefetches
+        # in a row are the normal use).
+        self._inflight[chunk_id] = (k, v, ev)
         return ev
 
 

@@ -17,6 +17,10 @@ from ._lib import AttnParams, KVCacheDesc, PrologueParams, check, lib
 
 HEAD_DIM = 128
 
+# Kernels of this library launched through this module since import (one entry, mutable): every wrapper below adds the
+# number of kernels its C entry point launches.  The benchmark reads the difference over its timed region.
+KERNEL_LAUNCHES = [0]
+
 
 class Context:
     """One per (device); owns the plan workspace.  Calls sharing a context must be stream-ordered."""
@@ -112,6 +116,7 @@ def qk_norm_rope(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tens
         p.rot_pairs, p.cos, p.sin = cos.shape[1], cos.data_ptr(), sin.data_ptr()
     keep = _fill_out(p, out, T, H, heads_per_block, block_out)
     check(lib.magi_qk_norm_rope_fwd(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
+    KERNEL_LAUNCHES[0] += 1
     return out
 
 
@@ -139,6 +144,7 @@ def head_block_copy(x: torch.Tensor, out: Optional[torch.Tensor], heads_per_bloc
         p.x, p.x_stride_t, p.x_stride_h, p.T, p.H = x.data_ptr(), x.stride(0), x.stride(1), T, H
     keep = _fill_out(p, out, T, H, heads_per_block, block_out)
     check(lib.magi_head_block_copy(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
+    KERNEL_LAUNCHES[0] += 1
     return out
 
 
@@ -243,7 +249,7 @@ def chunk_attn(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
                impl: str = "tcgen05", stream=None, q_scale: Optional[torch.Tensor] = None,
                k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None,
                scale_chunk_tokens: int = 0, q_lo: Optional[torch.Tensor] = None, o_peers=None,
-               out_heads_per_block: int = 0, out_block_stride: int = 0
+               out_heads_per_block: int = 0, out_block_stride: int = 0, ctx: Optional["Context"] = None
                ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """General entry: several k intervals per q-range (k_range_offsets) and a paged prefix.
 
@@ -251,12 +257,19 @@ def chunk_attn(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
 
     out_heads_per_block > 0 selects the head-block output layout: `out` is then a 2-D bf16 view [Tq, row_width]
     (stride(1) == 1) and head h lands at columns (h // hpb) * out_block_stride + (h % hpb) * 128, which is how
-    ProjInput (inference.py) has core and cross attention write the operand of the output projection in place."""
+    ProjInput (inference.py) has core and cross attention write the operand of the output projection in place.
+
+    ctx: the context whose plan workspace the call uses (default: the per-device shared one).  Calls that share a
+    context must be stream-ordered; a call that is meant to overlap another one on a side stream (cross-attention
+    beside the core attention) needs a Context of its own."""
     fp8 = q.dtype == torch.float8_e4m3fn
     in_dtype = torch.float8_e4m3fn if fp8 else torch.bfloat16
     _thd(q, "q", in_dtype)
     dev = q.device
-    ctx = Context.get(dev)
+    if ctx is None:
+        ctx = Context.get(dev)
+    elif ctx.device != dev.index:
+        raise ValueError("ctx belongs to another device")
     Tq, Hq, _ = q.shape
     p = AttnParams()
     p.struct_size = C.sizeof(AttnParams)
@@ -330,6 +343,7 @@ def chunk_attn(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
         p.cache, p.layer, p.n_prefix_chunks, p.prefix_chunk_ids = cache.handle, layer, len(prefix_chunk_ids), ids
     fn = {"tcgen05": lib.magi_chunk_attn_fwd, "simt": lib.magi_chunk_attn_fwd_simt}[impl]
     check(fn(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
+    KERNEL_LAUNCHES[0] += 2  # planner + attention kernel
     # qr/kr/ko are consumed by a kernel already enqueued on this stream; torch's caching allocator only
     # reuses their memory for later work on the same stream, so dropping them here is safe.
     return out, lse
@@ -350,6 +364,7 @@ def quantize_e4m3(x: torch.Tensor, chunk_tokens: int, stream=None, residual: boo
     check(lib.magi_quantize_e4m3_block128(ctx.handle, x.data_ptr(), x.stride(0), x.stride(1), T, H, int(chunk_tokens),
                                           x8.data_ptr(), lo.data_ptr() if residual else None, scales.data_ptr(),
                                           _stream(stream)), ctx.handle)
+    KERNEL_LAUNCHES[0] += 1
     return (x8, scales, lo) if residual else (x8, scales)
 
 

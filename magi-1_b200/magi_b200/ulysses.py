@@ -124,9 +124,18 @@ class UlyssesAttention:
     """Prologue + exchange + attention + exchange for one layer on one CP rank (CUDA)."""
 
     def __init__(self, cp_group, n_q_heads: int, n_kv_heads: int, split_sizes: Sequence[int], overlap_degree: int = 1,
-                 exchange: str = "torch"):
-        """exchange = "torch": torch.distributed all_to_all_single; "library": the library's own NCCL communicator."""
+                 exchange: str = "torch", head_order: str = "reference"):
+        """exchange = "torch": torch.distributed all_to_all_single; "library": the library's own NCCL communicator.
+
+        head_order matters only with overlap_degree > 1 on a rank that holds more than one KV head.  The reference
+        concatenates the outputs of the head groups (torch.cat(core_attn_outs, dim=1), context_parallel.py:594) before
+        the final rearrange, so inside each rank's block of the result the heads come group-major: (group i, kv head,
+        sub-head) instead of the projection's (kv head, group i, sub-head).  "reference" reproduces that order bit for
+        bit (what a drop-in must do); "original" keeps every head at its own global index."""
         from . import ops
+        if head_order not in ("reference", "original"):
+            raise ValueError("head_order must be 'reference' or 'original'")
+        self.head_order = head_order
         self.ops = ops
         self.ex = {"torch": UlyssesExchange, "library": LibraryExchange}[exchange](cp_group, split_sizes)
         cp = self.ex.cp
@@ -155,8 +164,11 @@ class UlyssesAttention:
     def forward(self, xq, xk, xv, gq, bq, gk, bk, cos, sin, q_ranges, k_ranges, max_seqlen_q, max_seqlen_k,
                 eps: float = 1e-6, norm_mode: str = "layernorm_1p", cache=None, layer: int = 0,
                 prefix_chunk_ids: Sequence[int] = (), k_range_offsets=None, attn_events: Optional[list] = None,
-                fp8_chunk_tokens: int = 0):
+                fp8_chunk_tokens: int = 0, cross_attn_func=None):
         """xq [s_local, Hq, 128], xk / xv [s_local, Hkv, 128]: this rank's tokens, all heads (projection outputs).
+        cross_attn_func: optional callable run after the last head group's attention has been enqueued, while its output
+        exchange is in flight (the cross-attention slot of the reference's schedule, context_parallel.py:591); forward
+        then returns (O, cross_attn_func()).
         cos / sin: this rank's rows of the rotary table.  Ranges are in full-sequence token coordinates.
         fp8_chunk_tokens > 0 runs the FP8 e4m3 attention: the head-sharded Q/K/V are block-quantised after the exchange
         (scale blocks counted from each multiple of fp8_chunk_tokens; Q and P carried as two terms), the exchange itself
@@ -209,8 +221,9 @@ class UlyssesAttention:
                 self._finish(pending, out, gsub)
             _, w = ex.gather_heads(o_full[i], o_recv[i])
             pending = (i, w, o_recv[i])
+        xattn_out = cross_attn_func() if cross_attn_func is not None else None
         self._finish(pending, out, gsub)
-        return out
+        return out if cross_attn_func is None else (out, xattn_out)
 
     def _finish(self, pending, out, gsub):
         """Wait for the exchange of head group i and place its blocks: "(cp sq) hn hd -> sq (cp hn) hd"."""
@@ -222,7 +235,10 @@ class UlyssesAttention:
             # group i holds sub-heads [i*gsub, (i+1)*gsub) of each local kv head: scatter them to their global positions
             cp, s_loc = o_recv.shape[0], o_recv.shape[1]
             g = self.hq_loc // self.hkv_loc
-            dst = out.view(s_loc, cp, self.hkv_loc, g, HEAD_DIM)[:, :, :, i * gsub:(i + 1) * gsub]
+            if self.head_order == "original":
+                dst = out.view(s_loc, cp, self.hkv_loc, g, HEAD_DIM)[:, :, :, i * gsub:(i + 1) * gsub]
+            else:  # the reference's cat over the groups: (group, kv head, sub-head) inside each rank's block
+                dst = out.view(s_loc, cp, self.overlap, self.hkv_loc, gsub, HEAD_DIM)[:, :, i]
             src = o_recv.view(cp, s_loc, self.hkv_loc, gsub, HEAD_DIM).permute(1, 0, 2, 3, 4)
             dst.copy_(src)
 
@@ -240,10 +256,15 @@ class FusedUlyssesAttention:
     multicast object, TMA only ever reads local memory.  Two tiny NCCL all-reduces per call act as stream-ordered
     barriers ("all receive buffers are complete", "all results are complete"); successive calls need nothing more, as
     a rank can only reach the next call's stores after every rank has passed the previous barrier.
-    The returned tensor is a view of this object's result buffer and is overwritten by the next call.
+    The returned tensor is a view of one of this object's n_out_buffers result buffers, used in rotation: it stays valid
+    until n_out_buffers further calls have been made (the reference returns a fresh tensor per call,
+    context_parallel.py:404-423; with two buffers a consumer of call i - a device-to-host copy, the output projection
+    on another stream - may still run while call i+1 computes, provided it has finished before this rank ENTERS call
+    i+2: every rank writes into the buffer only after the first barrier of that call, which this rank joins later).
     """
 
-    def __init__(self, cp_group, n_q_heads: int, n_kv_heads: int, split_sizes: Sequence[int], proj_hn: int = 0):
+    def __init__(self, cp_group, n_q_heads: int, n_kv_heads: int, split_sizes: Sequence[int], proj_hn: int = 0,
+                 n_out_buffers: int = 1):
         """proj_hn > 0 (8 in the reference): the result buffer is the operand of the output projection,
         [s_local, 2 * Hq * 128] in the "(hn n hd)" order of attn_linear_proj (dit_module.py:1332-1346); every rank's
         epilogue stores its heads at their final columns of the core-attention half, and cross_dest() gives the
@@ -276,31 +297,62 @@ class FusedUlyssesAttention:
             raise ValueError("the head count must be a multiple of proj_hn")
         self.proj_hn = int(proj_hn)
         self.o_row = (2 if proj_hn else 1) * self.hq * HEAD_DIM   # elements per token in a result buffer
-        self.buf_o = ops.PeerBuffer(s_max * self.o_row * 2, dev)
+        if n_out_buffers < 1:
+            raise ValueError("n_out_buffers must be at least 1")
+        self.bufs_o = [ops.PeerBuffer(s_max * self.o_row * 2, dev) for _ in range(n_out_buffers)]
         handles = [None] * cp
-        dist.all_gather_object(handles, (self.buf_q.handle, self.buf_kv.handle, self.buf_o.handle), group=cp_group)
-        self.peer_q, self.peer_kv, self.peer_o = [], [], []
+        dist.all_gather_object(handles, (self.buf_q.handle, self.buf_kv.handle, [b.handle for b in self.bufs_o]), group=cp_group)
+        self.peer_q, self.peer_kv, self.peers_o = [], [], [[] for _ in self.bufs_o]
         for r in range(cp):
             if r == self.rank:
-                self.peer_q.append(self.buf_q.ptr), self.peer_kv.append(self.buf_kv.ptr), self.peer_o.append(self.buf_o.ptr)
+                self.peer_q.append(self.buf_q.ptr), self.peer_kv.append(self.buf_kv.ptr)
+                for i, b in enumerate(self.bufs_o):
+                    self.peers_o[i].append(b.ptr)
             else:
                 hq_, hkv_, ho_ = handles[r]
                 self.peer_q.append(self.buf_q.open_peer(hq_))
                 self.peer_kv.append(self.buf_kv.open_peer(hkv_))
-                self.peer_o.append(self.buf_o.open_peer(ho_))
+                for i, b in enumerate(self.bufs_o):
+                    self.peers_o[i].append(b.open_peer(ho_[i]))
         self._flag = torch.zeros(1, dtype=torch.float32, device=torch.device("cuda", dev))
         self.q_recv = self.buf_q.as_tensor((S, self.hq_loc, HEAD_DIM))
         self.kv_recv = self.buf_kv.as_tensor((S, self.hkv_loc, 2 * HEAD_DIM))
-        self.out = self.buf_o.as_tensor((s_max, self.o_row) if proj_hn else (s_max, self.hq, HEAD_DIM))
+        self.outs = [b.as_tensor((s_max, self.o_row) if proj_hn else (s_max, self.hq, HEAD_DIM)) for b in self.bufs_o]
+        self._calls = 0
+        self._side = None      # stream and context of the cross-attention slot, created on first use
+        self._side_ctx = None
         self._barrier()
+
+    @property
+    def out(self) -> torch.Tensor:
+        """The result buffer of the most recent forward()."""
+        return self.outs[(self._calls - 1) % len(self.outs)]
+
+    @property
+    def peer_o(self) -> List[int]:
+        return self.peers_o[(self._calls - 1) % len(self.outs)]
 
     def _barrier(self):
         dist.all_reduce(self._flag, group=self.group)
 
     def forward(self, xq, xk, xv, gq, bq, gk, bk, cos, sin, q_ranges, k_ranges, max_seqlen_q, max_seqlen_k,
                 eps: float = 1e-6, norm_mode: str = "layernorm_1p", cache=None, layer: int = 0,
-                prefix_chunk_ids: Sequence[int] = (), k_range_offsets=None, attn_events: Optional[list] = None):
+                prefix_chunk_ids: Sequence[int] = (), k_range_offsets=None, attn_events: Optional[list] = None,
+                fp8_chunk_tokens: int = 0, kv_current_offset: int = 0, cross_attn_func=None):
+        """Arguments as UlyssesAttention.forward.  cache / prefix_chunk_ids: a head-sharded paged prefix (the cache holds
+        this rank's Hkv/cp heads, dit_module.py:794-798); the k ranges then address (prefix pages | current tokens).
+        kv_current_offset: the received K/V from this token on are the "current" keys (earlier tokens, if any, are
+        served by the prefix pages instead).
+        fp8_chunk_tokens > 0: the head-sharded Q/K/V are block-quantised to e4m3 after the exchange (Q as two terms) and
+        the FP8 kernel runs, with an fp8 cache if there is one; exchange and output stay bf16.
+        cross_attn_func(dest_kwargs, ctx): the cross-attention slot of the reference's schedule
+        (context_parallel.py:584-591).  It is called once the core attention is enqueued and runs on a side stream that
+        is current during the call, overlapping the result barrier; `ctx` is a Context of its own (two overlapping
+        attention calls must not share a plan workspace) to pass to ops.chunk_attn, and dest_kwargs (proj_hn > 0) are
+        the keyword arguments that store its heads into the other half of the projection operand.  forward then returns
+        (O, cross_attn_func's result) after the side stream has been joined."""
         ops = self.ops
+        self._calls += 1
         off = self.offsets[self.rank]
         kv_row = self.hkv_loc * 2 * HEAD_DIM   # elements per token in a kv receive buffer
         q_row = self.hq_loc * HEAD_DIM
@@ -314,15 +366,38 @@ class FusedUlyssesAttention:
         if attn_events is not None:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-        ops.chunk_attn(self.q_recv, self.kv_recv[..., :HEAD_DIM], self.kv_recv[..., HEAD_DIM:], q_ranges, k_ranges, max_seqlen_q,
+        q_in = self.q_recv
+        k_in, v_in = self.kv_recv[kv_current_offset:, :, :HEAD_DIM], self.kv_recv[kv_current_offset:, :, HEAD_DIM:]
+        fp8 = {}
+        if fp8_chunk_tokens > 0:
+            if kv_current_offset % fp8_chunk_tokens:
+                raise ValueError("kv_current_offset must be a multiple of fp8_chunk_tokens")
+            q_in, qs, q_lo = ops.quantize_e4m3(q_in, fp8_chunk_tokens, residual=True)
+            k_in, ks = ops.quantize_e4m3(k_in, fp8_chunk_tokens)
+            v_in, vs = ops.quantize_e4m3(v_in, fp8_chunk_tokens)
+            fp8 = dict(q_scale=qs, k_scale=ks, v_scale=vs, scale_chunk_tokens=fp8_chunk_tokens, q_lo=q_lo)
+        ops.chunk_attn(q_in, k_in, v_in, q_ranges, k_ranges, max_seqlen_q,
                        max_seqlen_k, return_lse=False, k_range_offsets=k_range_offsets, cache=cache, layer=layer,
                        prefix_chunk_ids=prefix_chunk_ids,
                        o_peers=(self.peer_o, self.offsets, self.rank * self.hq_loc, self.o_row, HEAD_DIM) + (
-                           (self.hq // self.proj_hn, 2 * (self.hq // self.proj_hn) * HEAD_DIM) if self.proj_hn else ()))
+                           (self.hq // self.proj_hn, 2 * (self.hq // self.proj_hn) * HEAD_DIM) if self.proj_hn else ()),
+                       **fp8)
         if attn_events is not None:
             e1.record()
             attn_events.append((e0, e1))
+        xattn_out = None
+        if cross_attn_func is not None:
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream()
+                self._side_ctx = ops.Context(torch.cuda.current_device())
+            self._side.wait_stream(main)   # the slot may read what the prologue / earlier work on the main stream produced
+            with torch.cuda.stream(self._side):
+                xattn_out = cross_attn_func(self.cross_dest() if self.proj_hn else {}, self._side_ctx)
         self._barrier()  # every rank's output rows have landed in every result buffer
+        if cross_attn_func is not None:
+            torch.cuda.current_stream().wait_stream(self._side)
+            return self.out[:self.s_loc], xattn_out
         return self.out[:self.s_loc]
 
     def cross_dest(self) -> dict:
@@ -337,5 +412,8 @@ class FusedUlyssesAttention:
         torch.cuda.synchronize()
         self._barrier()
         torch.cuda.synchronize()
-        for b in (self.buf_q, self.buf_kv, self.buf_o):
+        for b in [self.buf_q, self.buf_kv] + self.bufs_o:
             b.close()
+        if self._side_ctx is not None:
+            self._side_ctx.close()
+            self._side_ctx = None
