@@ -17,6 +17,14 @@ What is produced (all seeded, small enough to commit):
                  all_to_all_output_split, obtained by running them on gloo CPU ranks
                  (cp = 2 with an uneven split, cp = 4 with KV-head replication).
 
+  kranges.npz    the reference's k-range generators run as they are (SampleTransport.generate_default_kvrange,
+                 generate_noise2clean_kvrange, generate_kvrange_for_prefix_video, generate_kvrange_for_denoising_video,
+                 get_denoise_step_of_each_chunk, generate_sequences and VideoDiTModel.generate_kv_range_for_uncondition,
+                 executed from the reference's source files, with a SimpleNamespace standing in for `self`) over every
+                 forward step of the shipped 24B schedule and a few variations.
+  cp_xattn.npz   cp_ulysses_process (scatter_to_context_parallel_region of x / condition_map / rope +
+                 cp_update_cross_attn_qkv_range), and the scatter with cp_shuffle_num 2, run unmodified on gloo CPU ranks.
+
 The reference holds no attention fixture of its own; see the oracle's header.
 """
 import argparse
@@ -138,6 +146,166 @@ def gen_ulysses(ref_root, out_dir):
     np.savez_compressed(os.path.join(out_dir, "ulysses.npz"), **out)
 
 
+# ------------------------------------------------------------------------------------------------ k-range generators
+def _reference_functions(path, names):
+    """Compile the named functions / methods straight from a reference source file, without importing the module around
+    them (inference.pipeline.video_generate pulls in T5, the VAE and packages this container does not have).  The code
+    that runs is the reference's own text; nothing of it is stored here."""
+    import ast
+    from typing import Dict, List, Tuple, Union  # noqa: F401 - names the reference's annotations use
+    with open(path) as f:
+        tree = ast.parse(f.read())
+    found = {}
+    for node in ast.walk(tree):
+        if isinstance(node, ast.FunctionDef) and node.name in names and node.name not in found:
+            node.decorator_list = []
+            mod = ast.Module(body=[node], type_ignores=[])
+            ns = {"torch": torch, "List": List, "Tuple": Tuple, "Dict": Dict, "Union": Union, "np": np}
+            exec(compile(mod, path, "exec"), ns)
+            found[node.name] = ns[node.name]
+    missing = set(names) - set(found)
+    if missing:
+        raise RuntimeError(f"{path}: not found: {sorted(missing)}")
+    return found
+
+
+def gen_kranges(ref_root, out_dir):
+    vg = os.path.join(ref_root, "inference", "pipeline", "video_generate.py")
+    names = ["generate_sequences", "get_denoise_step_of_each_chunk", "get_batch_size_and_chunk_token_nums",
+             "generate_kvrange_for_prefix_video", "generate_default_kvrange", "generate_noise2clean_kvrange",
+             "generate_kvrange_for_denoising_video", "generate_denoise_status_and_sequences", "total_forward_step"]
+    fn = _reference_functions(vg, names)
+    out = {}
+
+    def make_self(num_steps, window_size, chunk_num, n2c, clean, prefix_chunks, batch=1, lat_h=90, lat_w=160):
+        prefix = torch.zeros(1, 1, prefix_chunks * 6, 1, 1) if prefix_chunks else None
+        ti = types.SimpleNamespace(latent_size=[1, 16, chunk_num * 6, lat_h, lat_w], num_steps=num_steps, chunk_num=chunk_num,
+                                   prefix_video=prefix)
+        me = types.SimpleNamespace(chunk_width=6, window_size=window_size, transport_inputs=[ti], device="cpu",
+                                   model_config=types.SimpleNamespace(patch_size=2),
+                                   runtime_config=types.SimpleNamespace(noise2clean_kvrange=list(n2c), clean_chunk_kvrange=clean))
+        for n in names[1:]:
+            setattr(me, n, types.MethodType(fn[n], me))
+        if batch != 1:   # the reference hard-codes batch 1; its range code nevertheless carries batch offsets
+            tok = me.get_batch_size_and_chunk_token_nums(0)[1]
+            me.get_batch_size_and_chunk_token_nums = lambda infer_idx: (batch, tok)
+        return me
+
+    # generate_denoise_status_and_sequences calls the module-level generate_sequences
+    fn["generate_denoise_status_and_sequences"].__globals__["generate_sequences"] = fn["generate_sequences"]
+
+    cases = {
+        # the shipped 24B base schedule (example/24B/24B_base_config.json): 32 steps, window 4, 96 frames -> 4 chunks
+        "base24b": dict(num_steps=32, window_size=4, chunk_num=4, n2c=[5, 4, 3, 2], clean=1, prefix_chunks=0),
+        # a longer clip so the steady state (4 chunks in flight, prefix behind them) is reached; distill schedule
+        "long16": dict(num_steps=16, window_size=4, chunk_num=9, n2c=[5, 4, 3, 2], clean=1, prefix_chunks=0),
+        # image/video-to-video: two prefix chunks; clean_chunk_kvrange -1 falls back to the last window
+        "prefix": dict(num_steps=8, window_size=4, chunk_num=7, n2c=[5, 4, 3, 2], clean=-1, prefix_chunks=2),
+        # no windows configured: every chunk sees everything before it
+        "default": dict(num_steps=8, window_size=4, chunk_num=5, n2c=[], clean=-1, prefix_chunks=0),
+        # batch offsets (k_batch_start = i * range_num)
+        "batch2": dict(num_steps=8, window_size=4, chunk_num=5, n2c=[3, 2], clean=1, prefix_chunks=0, batch=2),
+    }
+    for tag, c in cases.items():
+        me = make_self(**c)
+        rows = []
+        kr_all = []
+        for step in range(me.total_forward_step(0)):
+            (per_stage, stage, idx), (chunk_offset, chunk_start, chunk_end, t_start, t_end) = \
+                me.generate_denoise_status_and_sequences(0, step)
+            # slice_point / denoising_range_num / fwd_extra_1st_chunk as forward_velocity derives them (video_generate.py:606-628)
+            extra = chunk_start > chunk_offset and idx == 0
+            slice_point = chunk_start - 1 if extra else chunk_start
+            n_den = chunk_end - chunk_start + (1 if extra else 0)
+            steps_of = me.get_denoise_step_of_each_chunk(0, per_stage, t_start, t_end, idx, has_clean_t=extra)
+            kr = me.generate_kvrange_for_denoising_video(infer_idx=0, slice_point=slice_point, denoising_range_num=n_den,
+                                                         denoise_step_of_each_chunk=steps_of)
+            rows.append([step, chunk_offset, chunk_start, chunk_end, t_start, t_end, idx, int(extra), slice_point, n_den,
+                         len(kr_all)] + steps_of + [-1] * (8 - len(steps_of)))
+            kr_all.append(kr.numpy().astype(np.int32))
+        out[f"{tag}_cfg"] = np.array([c["num_steps"], c["window_size"], c["chunk_num"], c["clean"], c["prefix_chunks"],
+                                      c.get("batch", 1), me.get_batch_size_and_chunk_token_nums(0)[1]] + list(c["n2c"]))
+        out[f"{tag}_steps"] = np.array(rows, dtype=np.int32)
+        out[f"{tag}_kr_len"] = np.array([len(k) for k in kr_all], dtype=np.int32)
+        out[f"{tag}_kr"] = np.concatenate(kr_all)
+        for range_num in (1, 2, 7):
+            out[f"{tag}_prefix{range_num}"] = me.generate_kvrange_for_prefix_video(0, range_num).numpy().astype(np.int32)
+    # neither kind of window configured: generate_kvrange_for_prefix_video falls back to 8 chunks
+    me = make_self(num_steps=8, window_size=4, chunk_num=12, n2c=[], clean=-1, prefix_chunks=0)
+    out["fallback8_prefix12"] = me.generate_kvrange_for_prefix_video(0, 12).numpy().astype(np.int32)
+
+    # the unconditional pass: every chunk sees only itself, chunks laid out as batch (dit_model.py:92-101); the method asks
+    # for the current CUDA device, which this container does not have
+    from unittest import mock
+    un = _reference_functions(os.path.join(ref_root, "inference", "model", "dit", "dit_model.py"),
+                              ["generate_kv_range_for_uncondition"])["generate_kv_range_for_uncondition"]
+    real_to = torch.Tensor.to
+
+    def cpu_to(self, *a, **k):
+        a = tuple("cpu" if isinstance(x, str) and x.startswith("cuda") else x for x in a)
+        return real_to(self, *a, **k)
+    with mock.patch.object(torch.cuda, "current_device", lambda: 0), mock.patch.object(torch.Tensor, "to", cpu_to):
+        me = types.SimpleNamespace(model_config=types.SimpleNamespace(t_patch_size=1, patch_size=2))
+        out["uncond"] = un(me, torch.zeros(5, 16, 6, 90, 160)).numpy().astype(np.int32)
+    np.savez_compressed(os.path.join(out_dir, "kranges.npz"), **out)
+
+
+def _cp_xattn_worker(rank, world, ref_root, port, ret_dir):
+    sys.path.insert(0, ref_root)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from inference.common import PackedCrossAttnParams
+    from inference.infra.distributed import parallel_state as mpu
+    from inference.infra.parallelism import context_parallel as cp
+    mpu.initialize_model_parallel(cp_size=world)
+    out = {}
+
+    def params(chunk_tokens, n_ranges, caps):
+        cq = torch.arange(n_ranges + 1, dtype=torch.int32) * chunk_tokens
+        ck = torch.tensor([0] + list(np.cumsum(caps)), dtype=torch.int32)
+        return PackedCrossAttnParams(q_ranges=torch.stack([cq[:-1], cq[1:]], 1), kv_ranges=torch.stack([ck[:-1], ck[1:]], 1),
+                                     cu_seqlens_q=cq, cu_seqlens_kv=ck, max_seqlen_q=chunk_tokens, max_seqlen_kv=800)
+
+    # (a) cp_ulysses_process as the model calls it: x [S, N, D], condition_map [S], rope [S, 96]; batch 1 and batch 2
+    for tag, (C, n, N, caps) in {"a": (37, 3, 1, [5, 3, 9]), "b": (10, 5, 1, [4, 7, 3, 6, 2])}.items():
+        S = C * n
+        g = torch.Generator().manual_seed(21)
+        x = torch.randn(S, N, 8, generator=g)
+        cmap = torch.arange(S, dtype=torch.int32) // C
+        rope = torch.randn(S, 96, generator=g)
+        xs, cm, rp, splits, xp = cp.cp_ulysses_process(world, x, cmap, rope, None, params(C, n * N, caps))
+        out.update({f"{tag}_in": np.array([C, n, N] + caps), f"{tag}_x": xs.numpy(), f"{tag}_cmap": cm.numpy(), f"{tag}_rope": rp.numpy(),
+                    f"{tag}_splits": np.array(splits), f"{tag}_q": xp.q_ranges.numpy(), f"{tag}_k": xp.kv_ranges.numpy(),
+                    f"{tag}_maxq": np.array([xp.max_seqlen_q, xp.max_seqlen_kv])})
+    # (b) the scatter alone with a shuffled split (cp_shuffle_num 2, used by the reference's other CP strategy).  The range
+    # update is not run that way: with more than one batch element or shuffle piece its own closing assertion
+    # (unique q boundaries vs unique k boundaries) fails unless the surviving captions happen to be adjacent.
+    C, n, shuffle = 24, 4, 2
+    S = C * n
+    splits = [S // world] * world
+    out.update({"s_in": np.array([C, n, shuffle]), "s_splits": np.array(splits)})
+    g = torch.Generator().manual_seed(22)
+    x = torch.randn(S, 1, 4, generator=g)
+    out["s_x"] = cp.scatter_to_context_parallel_region(x, splits, cp_shuffle_num=shuffle).numpy()
+    np.savez(os.path.join(ret_dir, f"r{rank}.npz"), **out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def gen_cp_xattn(ref_root, out_dir):
+    import torch.multiprocessing as mp
+    out = {}
+    for world, port in ((2, 29621), (4, 29622)):
+        with tempfile.TemporaryDirectory() as td:
+            mp.spawn(_cp_xattn_worker, args=(world, ref_root, port, td), nprocs=world, join=True)
+            for r in range(world):
+                z = np.load(os.path.join(td, f"r{r}.npz"))
+                for key in z.files:
+                    out[f"cp{world}_r{r}_{key}"] = z[key]
+    np.savez_compressed(os.path.join(out_dir, "cp_xattn.npz"), **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", required=True, help="root of the MAGI-1 checkout")
@@ -156,6 +324,10 @@ def main():
         gen_attn_cfg0(a.out)
     if only is None or "ulysses" in only:
         gen_ulysses(a.ref, a.out)
+    if only is None or "kranges" in only:
+        gen_kranges(a.ref, a.out)
+    if only is None or "cp_xattn" in only:
+        gen_cp_xattn(a.ref, a.out)
     print("wrote fixtures to", a.out)
 
 

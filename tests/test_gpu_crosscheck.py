@@ -31,7 +31,7 @@ def test_against_sdpa_with_boolean_block_mask():
     from magi_b200 import host
     C, n, Hq, Hkv = 200, 3, 8, 2
     q, k, v = _inputs(C, n, Hq, Hkv, 91)
-    qr, kr = host.q_ranges_for_chunks(n, C), host.windowed_k_ranges(0, n, C, [2, 2, 1], 0)   # k-start > 0 for chunk 2
+    qr, kr = host.q_ranges_for_chunks(n, C), np.array([[0, C], [0, 2 * C], [2 * C, 3 * C]], dtype=np.int32)   # k-start > 0 for chunk 2
     out, _ = mb.chunk_attn(q.cuda(), k.cuda(), v.cuda(), qr, kr, C, n * C)
     mask = O.block_mask(qr, as_segments(kr), n * C, n * C).cuda()
     qf = q.cuda().float().permute(1, 0, 2)[None]                                    # [1, Hq, S, 128]

@@ -21,17 +21,71 @@ def test_rotary_table_matches_reference_fixture_and_oracle(golden_dir):
         assert torch.allclose(emb, torch.from_numpy(z[f"{name}_emb"]), atol=1e-6, rtol=0)
 
 
-def test_range_builders_match_oracle():
+def test_k_range_generators_match_the_reference_over_whole_schedules(golden_dir):
+    """host.generate_*_kvrange and host.denoise_schedule against kranges.npz: the reference's own generators run over every
+    forward step of the shipped 24B schedule, a longer clip, a prefix-video clip, the window-less default and batch 2."""
     from magi_b200 import host
+    z = np.load(f"{golden_dir}/kranges.npz")
+    for tag in ("base24b", "long16", "prefix", "default", "batch2"):
+        cfg = z[f"{tag}_cfg"].tolist()
+        num_steps, window_size, chunk_num, clean, prefix_chunks, batch, C = cfg[:7]
+        n2c = cfg[7:]
+        rows, kr, kr_len = z[f"{tag}_steps"], z[f"{tag}_kr"], z[f"{tag}_kr_len"]
+        starts = np.concatenate([[0], np.cumsum(kr_len)])
+        sched = list(host.denoise_schedule(num_steps, window_size, chunk_num, prefix_chunks))
+        assert len(sched) == len(rows)
+        for st, row in zip(sched, rows):
+            step, off, cs, ce, ts, te, idx, extra, sp, n_den, kidx = row[:11].tolist()
+            steps_of = [v for v in row[11:].tolist() if v >= 0]
+            assert (st["step"], st["chunk_start"], st["chunk_end"], int(st["fwd_extra_1st_chunk"]), st["slice_point"],
+                    st["denoising_range_num"], st["denoise_step_of_each_chunk"]) == (step, cs, ce, extra, sp, n_den, steps_of)
+            got = host.generate_kvrange_for_denoising_video(sp, n_den, steps_of, n2c, clean, num_steps, C, batch)
+            want = kr[starts[kidx]:starts[kidx + 1]]
+            assert got.dtype == np.int32 and np.array_equal(got, want), (tag, step, got, want)
+        for range_num in (1, 2, 7):
+            assert np.array_equal(host.generate_kvrange_for_prefix_video(range_num, C, clean, n2c, batch), z[f"{tag}_prefix{range_num}"])
+    assert np.array_equal(host.generate_kvrange_for_prefix_video(12, 21600), z["fallback8_prefix12"])
+    assert np.array_equal(host.generate_kv_range_for_uncondition(5, 21600), z["uncond"])
+    # the steady state of the shipped windows, as a readable instance: four chunks in flight at steps (24+i, 16+i, 8+i, i)
+    w = host.generate_noise2clean_kvrange(3, 4, [5, 4, 3, 2], 1, [25, 17, 9, 1], 32, 100)
+    assert w.tolist() == [[200, 400], [200, 500], [200, 600], [200, 700]]
+    # the same stage's first step re-forwards the chunk that just became clean: it sees only itself (clean_chunk_kvrange 1)
+    w = host.generate_noise2clean_kvrange(2, 5, [5, 4, 3, 2], 1, [32, 24, 16, 8, 0], 32, 100)
+    assert w.tolist() == [[200, 300], [200, 400], [200, 500], [200, 600], [200, 700]]
     assert np.array_equal(host.q_ranges_for_chunks(4, 9360), O.consecutive_q_ranges(4, 9360))
     for sp in (0, 1, 3):
         assert np.array_equal(host.default_k_ranges(4, 9360, sp), O.default_k_ranges(4, 9360, sp))
-    assert np.array_equal(host.windowed_k_ranges(6, 10, 100, [5, 4, 3, 2], 3), O.windowed_k_ranges(6, 10, 100, [5, 4, 3, 2], 3))
-    # steady state of the shipped schedule: windows end at each chunk and start > 0
-    w = host.windowed_k_ranges(6, 10, 100, [5, 4, 3, 2], 3)
-    assert w.tolist() == [[0, 400], [100, 500], [300, 600], [500, 700]]
     for s, cp in ((86400, 8), (37441, 4), (11, 2)):
         assert host.cp_split_sizes(s, cp) == O.cp_split_sizes(s, cp) and sum(host.cp_split_sizes(s, cp)) == s
+
+
+def test_cp_ulysses_process_matches_the_reference_on_gloo_ranks(golden_dir):
+    """host.cp_ulysses_process / scatter_to_context_parallel_region / cp_cross_attn_ranges against cp_xattn.npz: the
+    reference's cp_ulysses_process and scatter run unmodified on 2 and 4 gloo ranks."""
+    from magi_b200 import host
+    z = np.load(f"{golden_dir}/cp_xattn.npz")
+    for world in (2, 4):
+        for rank in range(world):
+            pre = f"cp{world}_r{rank}_"
+            for tag, seed in (("a", 21), ("b", 21)):
+                C, n, N, *caps = z[pre + f"{tag}_in"].tolist()
+                S = C * n
+                g = torch.Generator().manual_seed(seed)
+                x = torch.randn(S, N, 8, generator=g)
+                cmap = torch.arange(S, dtype=torch.int32) // C
+                rope = torch.randn(S, 96, generator=g)
+                qr, kr = host.cross_attn_ranges(C, n * N, caps)
+                xs, cm, rp, splits, (ql, kl, mq) = host.cp_ulysses_process(world, rank, x, cmap, rope, qr, kr)
+                assert splits == z[pre + f"{tag}_splits"].tolist()
+                assert torch.equal(xs, torch.from_numpy(z[pre + f"{tag}_x"])) and torch.equal(rp, torch.from_numpy(z[pre + f"{tag}_rope"]))
+                assert torch.equal(cm, torch.from_numpy(z[pre + f"{tag}_cmap"]))
+                assert np.array_equal(ql, z[pre + f"{tag}_q"]) and np.array_equal(kl, z[pre + f"{tag}_k"])
+                assert mq == int(z[pre + f"{tag}_maxq"][0])
+            C, n, shuffle = z[pre + "s_in"].tolist()
+            g = torch.Generator().manual_seed(22)
+            x = torch.randn(C * n, 1, 4, generator=g)
+            got = host.scatter_to_context_parallel_region(x, z[pre + "s_splits"].tolist(), rank, cp_shuffle_num=shuffle)
+            assert torch.equal(got, torch.from_numpy(z[pre + "s_x"]))
 
 
 def test_own_prefix_segments():
