@@ -571,6 +571,40 @@ def run_ours(args, wname, rank, world, local_rank, steps, warmup, want_e2e, want
     return res
 
 
+def bench_modulate(dev, rows, hidden, n_gates, peaks):
+    """The layer's gated post-norm residual (bias_modulate_add, dit_module.py:288-307) on the attention projection's
+    fp32 output at the workload's token count: HBM-bound, x (fp32) and the residual (bf16) read once, bf16 written once."""
+    import types
+    import magi_b200 as mb
+    g = torch.Generator(device=dev).manual_seed(9)
+    x = torch.randn(rows, hidden, generator=g, device=dev, dtype=torch.float32)
+    res = torch.randn(rows, hidden, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    gate = torch.tanh(torch.randn(n_gates, 2 * hidden, generator=g, device=dev)).to(torch.bfloat16)[:, :hidden]
+    cmap = torch.arange(rows, device=dev) * n_gates // rows
+    norm = types.SimpleNamespace(weight=0.1 * torch.randn(hidden, generator=g, device=dev), bias=torch.zeros(hidden, device=dev),
+                                 eps=1e-6, zero_centered_gamma=True)
+    out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
+    for _ in range(3):
+        mb.bias_modulate_add(x, res, cmap, gate, norm, out=out)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(5):
+        mb.bias_modulate_add(x, res, cmap, gate, norm, out=out)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 5
+    nbytes = rows * hidden * (4 + 2 + 2)
+    # spot check against the same arithmetic in torch on a few rows
+    idx = torch.tensor([0, rows // 2, rows - 1], device=dev)
+    y = x[idx] * gate[cmap[idx]].float()
+    ref = torch.nn.functional.layer_norm(y, (hidden,), norm.weight + 1, norm.bias, 1e-6) + res[idx].float()
+    err = float((out[idx].float() - ref).abs().max())
+    return {"kernel": "modulate_kernel", "bound": "hbm", "rows": rows, "hidden": hidden, "ms": ms, "algorithmic_bytes": nbytes,
+            "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "peak_gbs": peaks["hbm"], "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm"],
+            "max_abs_vs_torch_fp32_on_3_rows": err, "l2": "4.2 GB per launch, far beyond the 126 MB L2"}
+
+
 def flash_child(wname):
     """Child process of the default 1-GPU run: the reference's fallback dispatch on this GPU - a loop of flash_attn_func
     over the ranges (inference/model/dit/dit_module.py:1049-1065) with the flash-attn build of the image - on the same
@@ -691,6 +725,11 @@ def main():
         failed = not (r["parity"] and r["parity"]["ok"])
     r = None
     torch.cuda.empty_cache()
+    if world == 1 and rank == 0 and not args.no_other_configs:
+        C_ = w["H"] * w["W"] * w["frames_per_chunk"]
+        line["post_attention_modulate"] = bench_modulate(torch.device("cuda", local_rank), w["n_chunks"] * C_, w["hq"] * 128,
+                                                         w["n_chunks"], load_peaks())
+        torch.cuda.empty_cache()
 
     # ---- 1-GPU default run only: the other BASELINE configurations, a few steps each, and the reference's fallback
     # dispatch on this GPU (child process) - so that every configuration has a number on record beside the headline one

@@ -39,7 +39,7 @@ enum {
   MAGI_E_CUDA = -8      /* a CUDA runtime / driver call failed                                 */
 };
 
-enum { MAGI_DTYPE_BF16 = 0, MAGI_DTYPE_FP8_E4M3 = 1 };
+enum { MAGI_DTYPE_BF16 = 0, MAGI_DTYPE_FP8_E4M3 = 1, MAGI_DTYPE_F32 = 2 };
 enum { MAGI_NORM_LAYERNORM_1P = 0, MAGI_NORM_RMSNORM_1P = 1 };
 
 typedef struct magi_ctx magi_ctx;
@@ -248,6 +248,42 @@ MAGI_API int magi_chunk_attn_fwd_simt(magi_ctx* ctx, const magi_attn_params* p, 
  *     err/err_len (host buffer, may be NULL/0) receives the failure text. */
 MAGI_API int magi_chunk_attn_fwd_noalloc(const magi_attn_params* p, void* stream, int32_t* status_dev, char* err,
                                          int err_len);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Gated post-norm residual around the attention (and MLP) block.  Replaces bias_modulate_add
+ * (inference/model/dit/dit_module.py:288-307) and the Triton range_mod kernel inside it (:201-285), as called by
+ * TransformerLayer.gating_and_mlp (:1348-1367) on the output of the attention projection:
+ *     out[row] = post_norm( x[row] * gate[condition_map[row]] ) + residual[row]        (fp32 arithmetic, bf16 result)
+ * with post_norm = FusedLayerNorm over `hidden` (weight gamma, +1 when gamma_plus_one; :355-357).  One pass over HBM
+ * instead of the reference's x.float() / gating / layer_norm / add / cast passes.
+ * Rows are the flattened (batch, sequence) rows the reference forms with x.transpose(0, 1).flatten(0, 1); condition_map
+ * holds, per row, the row of `gate` (gatings.flatten(0, 1)) to use.  gamma == NULL skips the norm (plain range_mod),
+ * residual == NULL skips the add.  A map entry outside [0, n_gates) leaves that row unwritten and sets the context's
+ * device status word to MAGI_E_RANGE (read it with magi_ctx_status).
+ */
+typedef struct {
+  uint32_t struct_size;
+  int32_t x_dtype;              /* MAGI_DTYPE_BF16 or MAGI_DTYPE_F32 (the projection runs in fp32 when not quantised) */
+  const void* x;                /* [rows, hidden], row stride in elements                              */
+  int64_t x_stride;
+  const void* residual;         /* [rows, hidden] or NULL                                              */
+  int64_t residual_stride;
+  int32_t residual_dtype;       /* MAGI_DTYPE_BF16 or MAGI_DTYPE_F32                                   */
+  int32_t gate_dtype;           /* MAGI_DTYPE_BF16 or MAGI_DTYPE_F32                                   */
+  const void* gate;             /* [n_gates, hidden]; gate_stride lets it be one half of the fused (msa | mlp) gates */
+  int64_t gate_stride;
+  const void* condition_map;    /* device int32 or int64 [rows], or NULL (every row uses gate row 0)   */
+  int32_t map_is_int64;
+  int32_t n_gates;
+  const float* gamma;           /* fp32 [hidden] or NULL                                               */
+  const float* beta;            /* fp32 [hidden] or NULL                                               */
+  float eps;
+  int32_t gamma_plus_one;       /* the reference's apply_layernorm_1p                                  */
+  void* out;                    /* bf16 [rows, hidden]                                                 */
+  int64_t out_stride;
+  int32_t rows, hidden;         /* hidden: multiple of 8, at most 8192                                 */
+} magi_modulate_params;
+MAGI_API int magi_bias_modulate_add(magi_ctx* ctx, const magi_modulate_params* p, void* stream);
 
 /* Peer-visible device buffers for the fused Ulysses exchange: cudaMalloc + CUDA IPC (plain peer loads / stores over
  * NVLink; no multicast object is created).  magi_peer_alloc returns the local pointer and a 64-byte handle to hand to

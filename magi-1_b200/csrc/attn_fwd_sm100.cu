@@ -6,7 +6,7 @@
 // of the range's segments; tiles that the block mask excludes are never in the list.
 //
 //   warp 0      TMA producer: Q tiles once, then K_j, V_j into a ring of 32 KB stages
-//   warp 1      UMMA issuer (one thread): S_x = Q_x K_j^T, O_x += P_x V_j for the two Q tiles x = 0,1
+//   warps 1, 2  UMMA issuers (one thread each, one per Q tile x = 0,1): S_x = Q_x K_j^T, O_x += P_x V_j; they take turns
 //   warps 4-7   softmax for Q tile 0   } thread t of a warpgroup owns row t: TMEM lane = row, so row max /
 //   warps 8-11  softmax for Q tile 1   } row sum need no shuffles.  They also rescale O and store the output.
 //
@@ -15,6 +15,8 @@
 // While warpgroup 0 does softmax on S0 the tensor pipe runs the UMMAs of tile 1, and vice versa.
 #include <cuda_bf16.h>
 #include <math.h>
+#include <stdlib.h>
+
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -55,8 +57,8 @@ struct SmemLayout {
   static constexpr int kQ = 0;
   static constexpr int kRing = kQ + kTilesPerCta * kTileBytes;
   static constexpr int kBar = kRing + kStages * kTileBytes;
-  // barriers: q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2]
-  static constexpr int kNumBars = 1 + 2 * kStages + 6;
+  // barriers: q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2], turn[2]
+  static constexpr int kNumBars = 1 + 2 * kStages + 8;
   static constexpr int kMisc = kBar + kNumBars * 8;
   static constexpr int kTotal = kMisc + 16;
   static constexpr int kDynamic = kTotal + 1024;  // slack to align the base to 1024 bytes
@@ -72,6 +74,97 @@ __device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile_saddr, int k) {
   return umma_smem_desc(tile_saddr + k * 2048, kHalfBytes, 1024, kSw128);
 }
 
+// ---- softmax building blocks: one thread = one row; s[] holds the row's 128 scores (fp32 bits) and receives the bf16
+// weight pairs of columns [kC0, kC0 + kN) in s[kC0/2 .. (kC0 + kN)/2).
+template <int kC0, int kN>
+__device__ __forceinline__ void load_s_cols(uint32_t tS, uint32_t (&s)[kTileN], int valid) {
+#pragma unroll
+  for (int c = kC0; c < kC0 + kN; c += 32) tmem_ld32(tS + c, s + c);
+  tmem_wait_ld();
+  if (valid < kC0 + kN) {
+#pragma unroll
+    for (int c = kC0; c < kC0 + kN; ++c)
+      if (c >= valid) s[c] = 0xff800000u;  // -inf
+  }
+}
+
+// Fast path: exponentials against the maximum already baked into O and l; no maximum is computed.  A row whose scores
+// outgrew that reference shows in its row sum: above 128 * 2^8 (some weight is then above 2^8; inf and NaN also land
+// there) the tile is redone from the S still held in TMEM.  Scale-and-subtract and the row sum run as packed fp32 pairs
+// (half the instructions).  Returns the row sum.
+__device__ __forceinline__ float softmax_fast(uint32_t (&s)[kTileN], float sl2, float m_used) {
+  const float neg_m = -m_used * sl2;
+  uint64_t rs01 = f2_pack(0.f, 0.f), rs23 = rs01;
+  const uint64_t sl2_2 = f2_pack(sl2, sl2), neg_m2 = f2_pack(neg_m, neg_m);
+#pragma unroll
+  for (int c = 0; c < kTileN; c += 4) {
+    float x0, x1, x2, x3;
+    f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sl2_2, neg_m2), x0, x1);
+    f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), sl2_2, neg_m2), x2, x3);
+    const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(x2), p3 = ex2(x3);
+    rs01 = f2_add(rs01, f2_pack(p0, p1));
+    rs23 = f2_add(rs23, f2_pack(p2, p3));
+    s[c >> 1] = pack_bf16x2(p0, p1);
+    s[(c >> 1) + 1] = pack_bf16x2(p2, p3);
+  }
+  float r0, r1, r2, r3;
+  f2_unpack(rs01, r0, r1);
+  f2_unpack(rs23, r2, r3);
+  return (r0 + r2) + (r1 + r3);
+}
+
+// Exact path (first tile, or the running maximum moved): new reference maximum over these columns, then the
+// exponentials.  Rows that did not move by more than 2^8 keep their reference (alpha = 1).  Returns the row sum.
+template <int kC0, int kN>
+__device__ __forceinline__ float softmax_exact(uint32_t (&s)[kTileN], float sl2, float& m_used, float& alpha) {
+  float mxa[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) mxa[c] = __uint_as_float(s[kC0 + c]);
+#pragma unroll
+  for (int c = 8; c < kN; ++c) mxa[c & 7] = fmaxf(mxa[c & 7], __uint_as_float(s[kC0 + c]));
+  const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])), fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
+  const float m_new = fmaxf(m_used, mx);
+  const bool need = (m_new - m_used) * sl2 > 8.0f;
+  const float m_cur = need ? m_new : m_used;
+  alpha = need ? ex2((m_used - m_new) * sl2) : 1.0f;
+  const float neg_m = -m_cur * sl2;
+  float rs[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = kC0; c < kC0 + kN; c += 4) {
+    const float p0 = ex2(fmaf(__uint_as_float(s[c]), sl2, neg_m));
+    const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), sl2, neg_m));
+    const float p2 = ex2(fmaf(__uint_as_float(s[c + 2]), sl2, neg_m));
+    const float p3 = ex2(fmaf(__uint_as_float(s[c + 3]), sl2, neg_m));
+    rs[0] += p0;
+    rs[1] += p1;
+    rs[2] += p2;
+    rs[3] += p3;
+    s[c >> 1] = pack_bf16x2(p0, p1);
+    s[(c >> 1) + 1] = pack_bf16x2(p2, p3);
+  }
+  m_used = m_cur;
+  return (rs[0] + rs[2]) + (rs[1] + rs[3]);
+}
+
+__device__ __forceinline__ void rescale_o(uint32_t tO, float alpha) {
+#pragma unroll 1
+  for (int c4 = 0; c4 < 4; ++c4) {
+    uint32_t o[32];
+    tmem_ld32(tO + c4 * 32, o);
+    tmem_wait_ld();
+#pragma unroll
+    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+    tmem_st32(tO + c4 * 32, o);
+  }
+}
+
+// kDualIssuer: warps 1 and 2 each issue the UMMAs of one Q tile.  One thread issuing everything is the bottleneck of
+// the single-issuer form (a device timeline shows it 100 % busy: ~75 cycles per UMMA plus the barrier waits, fences and
+// commits around each batch, while the softmax warps wait for S half of the time).  Two threads overlap one tile's
+// waits and commits with the other tile's UMMA stream.  They pass a token (the `turn` barriers) so that the two tiles'
+// batches never interleave on the tensor pipe: interleaved batches complete together, which locks the two softmax
+// warpgroups in phase - both on the MUFU at once, then both waiting - and costs a third of the throughput.
+template <bool kDualIssuer>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
@@ -103,6 +196,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* s_full = kv_empty + kStages;
   uint64_t* p_full = s_full + 2;
   uint64_t* o_full = p_full + 2;
+  uint64_t* turn = o_full + 2;      // kDualIssuer: turn[x] = issuer x may put its next batch on the tensor pipe
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
 
@@ -110,12 +204,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(q_full, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&kv_empty[s], kDualIssuer ? 2 : 1);  // one commit per issuing thread that read the stage
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(&s_full[x], 1);
       mbar_init(&p_full[x], 4);  // one arrival per softmax warp: arrivals on one mbarrier serialise
       mbar_init(&o_full[x], 1);
+      mbar_init(&turn[x], 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -163,7 +258,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 1 || (kDualIssuer && warp == 2)) {
     // ------------------------------------------------------------------ UMMA issuer (one thread)
     // Order per K/V tile j:  PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1): while the tensor pipe works for one Q tile the
     // other tile's warpgroup does its softmax.  The loop is kept to a few instructions per UMMA (a single thread
@@ -201,14 +296,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto advance = [&]() {
         if (++stage == kStages) { stage = 0; parity ^= 1; }
       };
+      // tiles this thread issues for: both (single issuer) or its own
+      const int x_lo = kDualIssuer ? warp - 1 : 0, x_hi = kDualIssuer ? warp : 2;
       bool ok = mbar_wait(q_full, 0, abort_flag);
       ok = ok && mbar_wait(&kv_full[stage], parity, abort_flag);
+      if (kDualIssuer && ok && x_lo == 1) ok = mbar_wait(&turn[1], 0, abort_flag);
       if (ok) {
         tc_fence_after_sync();
-        issue_qk(0, stage);
-        umma_commit(&s_full[0]);
-        issue_qk(1, stage);
-        umma_commit(&s_full[1]);
+        for (int x = x_lo; x < x_hi; ++x) {
+          issue_qk(x, stage);
+          if (kDualIssuer) mbar_arrive(&turn[1 - x]);
+          umma_commit(&s_full[x]);
+        }
         umma_commit(&kv_empty[stage]);
         advance();
       }
@@ -222,17 +321,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (more) advance();
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
+          if (kDualIssuer && x != x_lo) continue;
+          if (!ok) break;
+          // the token first: turn[0] completes a phase after the other thread's batch j-1 (and once in the prologue),
+          // turn[1] after this tile-0 thread's batch j
+          if (kDualIssuer) ok = mbar_wait(&turn[x], (uint32_t)(j + x) & 1, abort_flag);
           if (!ok) break;
           ok = mbar_wait(&p_full[x], j & 1, abort_flag);
           if (!ok) break;
           tc_fence_after_sync();
           issue_pv(x, v_stage, j == 0);
-          if (!more) umma_commit(&o_full[x]);  // only the epilogue waits for O (a later S_x implies the earlier PV_x)
-          if (x == 1) umma_commit(&kv_empty[v_stage]);
-          if (more) {
-            issue_qk(x, k_stage);
-            umma_commit(&s_full[x]);
-            if (x == 1) umma_commit(&kv_empty[k_stage]);
+          if constexpr (kDualIssuer) {
+            if (more) issue_qk(x, k_stage);
+            mbar_arrive(&turn[1 - x]);  // the batch is on the pipe: the other tile's may follow
+            if (more) umma_commit(&s_full[x]);
+            else umma_commit(&o_full[x]);
+            umma_commit(&kv_empty[v_stage]);
+            if (more) umma_commit(&kv_empty[k_stage]);
+          } else {
+            if (!more) umma_commit(&o_full[x]);  // only the epilogue waits for O (a later S_x implies the earlier PV_x)
+            if (x == 1) umma_commit(&kv_empty[v_stage]);
+            if (more) {
+              issue_qk(x, k_stage);
+              umma_commit(&s_full[x]);
+              if (x == 1) umma_commit(&kv_empty[k_stage]);
+            }
           }
         }
       }
@@ -260,93 +373,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_after_sync();
         // S_x(j) complete implies PV_x(j-1) complete (same issuing thread, in order), so O_x may be rescaled here.
         uint32_t s[kTileN];
-        auto load_s = [&]() {
-          tmem_ld32(tS, s);
-          tmem_ld32(tS + 32, s + 32);
-          tmem_ld32(tS + 64, s + 64);
-          tmem_ld32(tS + 96, s + 96);
-          tmem_wait_ld();
-          if (valid < kTileN) {
-#pragma unroll
-            for (int c = 0; c < kTileN; ++c)
-              if (c >= valid) s[c] = 0xff800000u;  // -inf
-          }
-        };
-        load_s();
+        load_s_cols<0, kTileN>(tS, s, valid);
         float alpha = 1.0f, rowsum = 0.f;
         bool redo = (j == 0);
         if (j > 0) {
-          // Fast path: exponentials against the maximum already baked into O and l; no maximum is computed.  A row
-          // whose scores outgrew that reference shows in its row sum: above 128 * 2^8 (some weight is then above 2^8;
-          // inf and NaN also land here) the tile is redone below from the S still held in TMEM.  Scale-and-subtract
-          // and the row sum run as packed fp32 pairs (half the instructions; the chain is issue-bound, not MUFU-bound).
-          const float neg_m = -m_used * sl2;
-          uint64_t rs01 = f2_pack(0.f, 0.f), rs23 = rs01;
-          const uint64_t sl2_2 = f2_pack(sl2, sl2), neg_m2 = f2_pack(neg_m, neg_m);
-#pragma unroll
-          for (int c = 0; c < kTileN; c += 4) {
-            float x0, x1, x2, x3;
-            f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sl2_2, neg_m2), x0, x1);
-            f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), sl2_2, neg_m2), x2, x3);
-            const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(x2), p3 = ex2(x3);
-            rs01 = f2_add(rs01, f2_pack(p0, p1));
-            rs23 = f2_add(rs23, f2_pack(p2, p3));
-            s[c >> 1] = pack_bf16x2(p0, p1);
-            s[(c >> 1) + 1] = pack_bf16x2(p2, p3);
-          }
-          {
-            float r0, r1, r2, r3;
-            f2_unpack(rs01, r0, r1);
-            f2_unpack(rs23, r2, r3);
-            rowsum = (r0 + r2) + (r1 + r3);
-          }
+          rowsum = softmax_fast(s, sl2, m_used);
           redo = __any_sync(0xffffffffu, !(rowsum <= kRedoRowSum));
-          if (redo) load_s();
+          if (redo) load_s_cols<0, kTileN>(tS, s, valid);
         }
-        if (redo) {
-          // Exact path (first tile, or the running maximum moved): new reference maximum, then the exponentials.
-          float mxa[8];
-#pragma unroll
-          for (int c = 0; c < 8; ++c) mxa[c] = __uint_as_float(s[c]);
-#pragma unroll
-          for (int c = 8; c < kTileN; ++c) mxa[c & 7] = fmaxf(mxa[c & 7], __uint_as_float(s[c]));
-          const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
-                                 fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
-          const float m_new = fmaxf(m_used, mx);
-          const bool need = (m_new - m_used) * sl2 > 8.0f;  // rows that did not move keep their reference maximum
-          const float m_cur = need ? m_new : m_used;
-          alpha = need ? ex2((m_used - m_new) * sl2) : 1.0f;
-          const float neg_m = -m_cur * sl2;
-          float rs[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int c = 0; c < kTileN; c += 4) {
-            const float p0 = ex2(fmaf(__uint_as_float(s[c]), sl2, neg_m));
-            const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), sl2, neg_m));
-            const float p2 = ex2(fmaf(__uint_as_float(s[c + 2]), sl2, neg_m));
-            const float p3 = ex2(fmaf(__uint_as_float(s[c + 3]), sl2, neg_m));
-            rs[0] += p0;
-            rs[1] += p1;
-            rs[2] += p2;
-            rs[3] += p3;
-            s[c >> 1] = pack_bf16x2(p0, p1);
-            s[(c >> 1) + 1] = pack_bf16x2(p2, p3);
-          }
-          rowsum = (rs[0] + rs[2]) + (rs[1] + rs[3]);
-          m_used = m_cur;
-        }
+        if (redo) rowsum = softmax_exact<0, kTileN>(s, sl2, m_used, alpha);
         tmem_st32(tS, s);
         tmem_st32(tS + 32, s + 32);
-        if (redo && j > 0) {
-#pragma unroll 1
-          for (int c4 = 0; c4 < 4; ++c4) {
-            uint32_t o[32];
-            tmem_ld32(tO + c4 * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-            tmem_st32(tO + c4 * 32, o);
-          }
-        }
+        if (redo && j > 0) rescale_o(tO, alpha);
         l = l * alpha + rowsum;
         tmem_wait_st();
         tc_fence_before_sync();
@@ -416,7 +454,8 @@ int attn_fp8_init_device(magi_ctx* ctx);
 // Opt in to > 48 KB of dynamic shared memory; called once per context with its device current.
 int attn_init_device(magi_ctx* ctx) {
   if (int rc = attn_fp8_init_device(ctx)) return rc;
-  MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::kDynamic));
+  MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::kDynamic));
+  MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::kDynamic));
   return MAGI_OK;
 }
 
@@ -456,7 +495,10 @@ int launch_attn_bf16(magi_ctx* ctx, const magi_attn_params* p, int max_items, cu
   fill_peer_table(kp, p);
 
   dim3 grid(max_items, p->n_q_heads, 1);
-  attn_fwd_kernel<<<grid, kAttnThreads, SmemLayout::kDynamic, stream>>>(tq, tk, tv, tkc, tvc, kp);
+  // MAGI_ATTN_SINGLE_ISSUER=1 selects the one-thread issuer (kept for A/B measurements; about 2 % slower)
+  const char* v = getenv("MAGI_ATTN_SINGLE_ISSUER");
+  if (v && v[0] == '1') attn_fwd_kernel<false><<<grid, kAttnThreads, SmemLayout::kDynamic, stream>>>(tq, tk, tv, tkc, tvc, kp);
+  else attn_fwd_kernel<true><<<grid, kAttnThreads, SmemLayout::kDynamic, stream>>>(tq, tk, tv, tkc, tvc, kp);
   MAGI_CUDA_OK(ctx, cudaGetLastError());
   return MAGI_OK;
 }

@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(_HERE, "libmagi_attn.so")
 
 MAGI_OK = 0
 E_BADARG, E_ALIGN, E_ARCH, E_RANGE, E_NOMEM, E_NCCL, E_TIMEOUT, E_CUDA = -1, -2, -3, -4, -5, -6, -7, -8
-DTYPE_BF16, DTYPE_FP8_E4M3 = 0, 1
+DTYPE_BF16, DTYPE_FP8_E4M3, DTYPE_F32 = 0, 1, 2
 NORM_LAYERNORM_1P, NORM_RMSNORM_1P = 0, 1
 
 EXPORTS = [
@@ -19,6 +19,7 @@ EXPORTS = [
     "magi_kv_cache_append", "magi_kv_cache_evict", "magi_kv_cache_read", "magi_kv_cache_bytes",
     "magi_chunk_attn_fwd", "magi_chunk_attn_fwd_simt", "magi_quantize_e4m3_block128", "magi_chunk_attn_fwd_noalloc",
     "magi_peer_alloc", "magi_peer_open", "magi_peer_close", "magi_peer_free", "magi_selftest_bounded_wait",
+    "magi_bias_modulate_add",
     "magi_ulysses_unique_id", "magi_ulysses_create", "magi_ulysses_destroy", "magi_ulysses_a2a_in", "magi_ulysses_a2a_out",
 ]
 
@@ -65,6 +66,19 @@ class AttnParams(C.Structure):
     ]
 
 
+class ModulateParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("x_dtype", C.c_int32),
+        ("x", C.c_void_p), ("x_stride", C.c_int64),
+        ("residual", C.c_void_p), ("residual_stride", C.c_int64),
+        ("residual_dtype", C.c_int32), ("gate_dtype", C.c_int32),
+        ("gate", C.c_void_p), ("gate_stride", C.c_int64),
+        ("condition_map", C.c_void_p), ("map_is_int64", C.c_int32), ("n_gates", C.c_int32),
+        ("gamma", C.c_void_p), ("beta", C.c_void_p), ("eps", C.c_float), ("gamma_plus_one", C.c_int32),
+        ("out", C.c_void_p), ("out_stride", C.c_int64), ("rows", C.c_int32), ("hidden", C.c_int32),
+    ]
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -96,6 +110,7 @@ def _load():
         "magi_chunk_attn_fwd_simt": (C.c_int, [vp, C.POINTER(AttnParams), vp]),
         "magi_quantize_e4m3_block128": (C.c_int, [vp, vp, i64, i64, i32, i32, i32, vp, vp, vp, vp]),
         "magi_chunk_attn_fwd_noalloc": (C.c_int, [C.POINTER(AttnParams), vp, vp, C.c_char_p, i32]),
+        "magi_bias_modulate_add": (C.c_int, [vp, C.POINTER(ModulateParams), vp]),
         "magi_peer_alloc": (C.c_int, [vp, C.c_uint64, C.POINTER(vp), C.c_char_p]),
         "magi_peer_open": (C.c_int, [vp, C.c_char_p, C.POINTER(vp)]),
         "magi_peer_close": (C.c_int, [vp, vp]),

@@ -169,6 +169,15 @@ class ProjInput:
         return x.view(sq, 2, hn, -1).permute(0, 2, 1, 3).reshape(sq, -1).contiguous()  # (hn n hd)
 
 
+def bias_modulate_add(x: torch.Tensor, residual: torch.Tensor, condition_map: torch.Tensor, gate: torch.Tensor, post_norm):
+    """Same name and arguments as the reference's bias_modulate_add (inference/model/dit/dit_module.py:288-307), called
+    by TransformerLayer.gating_and_mlp (:1348-1367) on the attention projection's output and again after the MLP:
+    x, residual [s, b, h]; condition_map [s, b]; gate [b, denoising_range_num, h] (one half of the soft-capped adaLN
+    gates); post_norm: the layer's FusedLayerNorm.  One kernel, bf16 result (the reference casts to params_dtype right
+    after the call)."""
+    return ops.bias_modulate_add(x, residual, condition_map, gate, post_norm)
+
+
 class ChunkCausalSelfAttention:
     """One layer's self-attention core: prologue -> KV-cache gate -> chunk-causal attention."""
 

@@ -13,7 +13,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import AttnParams, KVCacheDesc, PrologueParams, check, lib
+from ._lib import AttnParams, KVCacheDesc, ModulateParams, PrologueParams, check, lib
 
 HEAD_DIM = 128
 
@@ -366,6 +366,59 @@ def quantize_e4m3(x: torch.Tensor, chunk_tokens: int, stream=None, residual: boo
                                           _stream(stream)), ctx.handle)
     KERNEL_LAUNCHES[0] += 1
     return (x8, scales, lo) if residual else (x8, scales)
+
+
+def bias_modulate_add(x: torch.Tensor, residual: Optional[torch.Tensor], condition_map: Optional[torch.Tensor],
+                      gate: torch.Tensor, post_norm=None, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """out = post_norm(x.float() * gate[condition_map]) + residual.float(), as bf16 - the reference's bias_modulate_add
+    (inference/model/dit/dit_module.py:288-307) in one kernel.
+
+    x [s, b, h] or [rows, h], bf16 or fp32; residual like x (bf16 or fp32) or None; condition_map [s, b] / [rows] int32 or
+    int64 (None: gate row 0 everywhere); gate [b, n, h] or [n_gates, h], bf16 or fp32, last dim contiguous (a chunk of
+    the fused gates is fine); post_norm: an object with weight, bias, eps and zero_centered_gamma (the reference's
+    FusedLayerNorm), or None for the gating alone.  For b > 1 the rows are taken batch-major, as the reference's
+    x.transpose(0, 1).flatten(0, 1) does, and the result comes back in x's shape."""
+    dt = {torch.bfloat16: _lib.DTYPE_BF16, torch.float32: _lib.DTYPE_F32}
+    shape = x.shape
+    if x.dim() == 3:
+        if x.shape[1] != 1:
+            raise ValueError("batch > 1: pass x, residual and condition_map already flattened batch-major to [rows, h]")
+        x = x[:, 0]
+        residual = residual[:, 0] if residual is not None else None
+        condition_map = condition_map[:, 0] if condition_map is not None else None
+    if gate.dim() == 3:
+        if gate.shape[0] != 1 and not gate.is_contiguous():
+            raise ValueError("gate [b, n, h] with b > 1 must be contiguous")
+        gate = gate.reshape(-1, gate.shape[-1]) if gate.is_contiguous() else gate[0]
+    for name, t in (("x", x), ("gate", gate)) + ((("residual", residual),) if residual is not None else ()):
+        if not t.is_cuda or t.dtype not in dt or t.dim() != 2 or t.stride(1) != 1:
+            raise ValueError(f"{name} must be a CUDA bf16/fp32 matrix with a contiguous last dim")
+    rows, h = x.shape
+    ctx = Context.get(x.device)
+    if out is None:
+        out = torch.empty(rows, h, dtype=torch.bfloat16, device=x.device)
+    p = ModulateParams()
+    p.struct_size = C.sizeof(ModulateParams)
+    p.x, p.x_stride, p.x_dtype = x.data_ptr(), x.stride(0), dt[x.dtype]
+    if residual is not None:
+        p.residual, p.residual_stride, p.residual_dtype = residual.data_ptr(), residual.stride(0), dt[residual.dtype]
+    p.gate, p.gate_stride, p.gate_dtype, p.n_gates = gate.data_ptr(), gate.stride(0), dt[gate.dtype], gate.shape[0]
+    if condition_map is not None:
+        if condition_map.dtype not in (torch.int32, torch.int64) or condition_map.numel() != rows:
+            raise ValueError("condition_map must be int32 or int64 with one entry per row")
+        condition_map = condition_map.contiguous()
+        p.condition_map, p.map_is_int64 = condition_map.data_ptr(), int(condition_map.dtype == torch.int64)
+    keep = None
+    if post_norm is not None:
+        gamma = post_norm.weight.detach().to(device=x.device, dtype=torch.float32).contiguous()
+        beta = post_norm.bias.detach().to(device=x.device, dtype=torch.float32).contiguous() if getattr(post_norm, "bias", None) is not None else None
+        keep = (gamma, beta)
+        p.gamma, p.beta = gamma.data_ptr(), beta.data_ptr() if beta is not None else None
+        p.eps, p.gamma_plus_one = float(post_norm.eps), int(bool(getattr(post_norm, "zero_centered_gamma", False)))
+    p.out, p.out_stride, p.rows, p.hidden = out.data_ptr(), out.stride(0), rows, h
+    check(lib.magi_bias_modulate_add(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
+    KERNEL_LAUNCHES[0] += 1
+    return out.view(shape) if len(shape) == 3 else out
 
 
 class PeerBuffer:

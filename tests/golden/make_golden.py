@@ -25,6 +25,10 @@ What is produced (all seeded, small enough to commit):
   cp_xattn.npz   cp_ulysses_process (scatter_to_context_parallel_region of x / condition_map / rope +
                  cp_update_cross_attn_qkv_range), and the scatter with cp_shuffle_num 2, run unmodified on gloo CPU ranks.
 
+  modulate.npz   the reference's bias_modulate_add (dit_module.py:288-307) with its own FusedLayerNorm, the Triton gating
+                 kernel inside it replaced by the one-line torch statement of what it computes (y[row] = x[row] *
+                 gate[map[row]]: Triton needs a GPU), for an fp32 and a bf16 projection output.
+
 The reference holds no attention fixture of its own; see the oracle's header.
 """
 import argparse
@@ -306,6 +310,33 @@ def gen_cp_xattn(ref_root, out_dir):
     np.savez_compressed(os.path.join(out_dir, "cp_xattn.npz"), **out)
 
 
+def gen_modulate(ref_mod, out_dir):
+    def range_mod_torch(x, c_mapping, gatings):   # what range_mod_triton returns, on the CPU
+        s, b, h = x.shape
+        xf = x.transpose(0, 1).flatten(0, 1)
+        y = xf * gatings.flatten(0, 1)[c_mapping.transpose(0, 1).flatten(0, 1).long()]
+        return y.reshape(b, s, h).transpose(0, 1)
+    ref_mod.range_mod_triton = range_mod_torch
+    out = {}
+    for tag, (S, n, h, xdt) in {"f32": (24, 3, 512, torch.float32), "bf16": (16, 2, 1536, torch.bfloat16)}.items():
+        g = torch.Generator().manual_seed(31 + h)
+        cfg = types.SimpleNamespace(apply_layernorm_1p=True, layernorm_epsilon=1e-6, params_dtype=torch.float32)
+        ln = ref_mod.FusedLayerNorm(cfg, h)
+        with torch.no_grad():
+            ln.weight.copy_(0.1 * torch.randn(h, generator=g))
+            ln.bias.copy_(0.05 * torch.randn(h, generator=g))
+        x = (torch.randn(S, 1, h, generator=g) * 3 + 0.5).to(xdt)
+        res = torch.randn(S, 1, h, generator=g).to(torch.bfloat16)
+        gate = torch.tanh(torch.randn(1, n, 2 * h, generator=g)).to(torch.bfloat16)   # soft-capped adaLN gates, msa | mlp
+        cmap = (torch.arange(S) * n // S).reshape(S, 1)                               # int64, as torch.arange gives
+        with torch.no_grad():
+            y = ref_mod.bias_modulate_add(x, res, cmap, gate.chunk(2, dim=-1)[1], ln).to(torch.bfloat16)
+        out.update({f"{tag}_x": x.float().numpy() if xdt == torch.float32 else bf16_bits(x), f"{tag}_res": bf16_bits(res),
+                    f"{tag}_gate": bf16_bits(gate), f"{tag}_cmap": cmap.numpy(), f"{tag}_gamma": ln.weight.detach().numpy(),
+                    f"{tag}_beta": ln.bias.detach().numpy(), f"{tag}_out": bf16_bits(y)})
+    np.savez_compressed(os.path.join(out_dir, "modulate.npz"), **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", required=True, help="root of the MAGI-1 checkout")
@@ -314,12 +345,14 @@ def main():
     a = ap.parse_args()
     sys.path.insert(0, a.ref)
     only = set(a.only.split(",")) if a.only else None
-    if only is None or "prologue" in only or "rope" in only:
+    if only is None or "prologue" in only or "rope" in only or "modulate" in only:
         import inference.model.dit.dit_module as ref_mod
         if only is None or "prologue" in only:
             gen_prologue(ref_mod, a.out)
         if only is None or "rope" in only:
             gen_rope(ref_mod, a.out)
+        if only is None or "modulate" in only:
+            gen_modulate(ref_mod, a.out)
     if only is None or "attn" in only:
         gen_attn_cfg0(a.out)
     if only is None or "ulysses" in only:

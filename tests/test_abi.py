@@ -50,6 +50,8 @@ def test_struct_layouts_match_the_header(tmp_path):
         "magi_prologue_params": ["x", "T", "gamma", "eps", "cos", "out", "out_stride_block", "heads_per_block",
                                  "out_block_ptrs", "x_heads_per_block", "x_stride_block"],
         "magi_kv_cache_desc": ["dtype", "chunk_tokens", "n_kv_heads"],
+        "magi_modulate_params": ["x", "residual", "residual_dtype", "gate", "gate_stride", "condition_map", "n_gates", "gamma",
+                                 "eps", "gamma_plus_one", "out", "out_stride", "rows", "hidden"],
     }
     body = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]
     for s, fs in fields.items():
@@ -61,7 +63,8 @@ def test_struct_layouts_match_the_header(tmp_path):
     exe = tmp_path / "probe"
     subprocess.check_call(["gcc", str(probe), "-o", str(exe)])
     out = subprocess.check_output([str(exe)], text=True).split("\n")
-    mirror = {"magi_attn_params": L.AttnParams, "magi_prologue_params": L.PrologueParams, "magi_kv_cache_desc": L.KVCacheDesc}
+    mirror = {"magi_attn_params": L.AttnParams, "magi_prologue_params": L.PrologueParams, "magi_kv_cache_desc": L.KVCacheDesc,
+              "magi_modulate_params": L.ModulateParams}
     for line in out:
         if not line:
             continue

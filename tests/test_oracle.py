@@ -124,3 +124,18 @@ def test_e4m3_block_quantiser_roundtrip():
     back = O.dequantize_e4m3_block128(x8, sc, spans)
     assert O.cosine(back, x) > 0.999
     assert (back - x).abs().max() <= x.abs().max() / 16 + 1e-6
+
+
+def test_bias_modulate_add_matches_reference_fixture(golden_dir):
+    """oracle.bias_modulate_add against modulate.npz: the reference's bias_modulate_add + FusedLayerNorm run on the CPU."""
+    z = np.load(f"{golden_dir}/modulate.npz")
+    bf = lambda a: torch.from_numpy(a.copy()).view(torch.bfloat16)
+    for tag in ("f32", "bf16"):
+        x = torch.from_numpy(z[f"{tag}_x"]) if tag == "f32" else bf(z[f"{tag}_x"])
+        res, gate, want = bf(z[f"{tag}_res"]), bf(z[f"{tag}_gate"]), bf(z[f"{tag}_out"])
+        h = x.shape[-1]
+        got = O.bias_modulate_add(x, res, torch.from_numpy(z[f"{tag}_cmap"]), gate[..., h:], torch.from_numpy(z[f"{tag}_gamma"]),
+                                  torch.from_numpy(z[f"{tag}_beta"])).to(torch.bfloat16)
+        diff = (got.float() - want.float()).abs()
+        assert (diff <= want.float().abs() * 2 ** -7 + 1e-6).all(), f"{tag}: more than one bf16 ulp off ({diff.max().item()})"
+        assert (got.view(torch.int16) == want.view(torch.int16)).float().mean().item() > 0.99
