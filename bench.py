@@ -561,7 +561,7 @@ def run_ours(args, wname, rank, world, local_rank, steps, warmup, want_e2e, want
         if prologue_ev:
             pms = sum(a.elapsed_time(b) for a, b in prologue_ev) / len(prologue_ev)
             pbytes = 2 * xq.numel() * 2 + 2 * cos.numel() * 4  # bf16 read + bf16 write of Q, cos+sin once
-            res["prologue_q"] = {"kernel": "prologue16_kernel", "bound": "hbm", "ms": pms, "algorithmic_bytes": pbytes,
+            res["prologue_q"] = {"kernel": "prologue8_kernel", "bound": "hbm", "ms": pms, "algorithmic_bytes": pbytes,
                                  "achieved_gbs": pbytes / (pms * 1e-3) / 1e9, "peak_gbs": peaks["hbm"],
                                  "frac": pbytes / (pms * 1e-3) / 1e9 / peaks["hbm"]}
         if fp8:
@@ -664,12 +664,18 @@ def main():
                     help="1 GPU: do not time the reference's flash_attn_func fallback loop in a child process")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: Ulysses exchange fused into the kernels over peer memory, or NCCL all-to-all + copies")
+    ap.add_argument("--modulate-only", type=int, default=0, metavar="ROWS",
+                    help="time only the gated post-norm residual kernel on ROWS rows of the workload's hidden size and print its block")
     ap.add_argument("--flash-child", default=None, help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.flash_child:
         flash_child(args.flash_child)
         return
     w = WORKLOADS[args.workload]
+    if args.modulate_only:
+        torch.cuda.set_device(0)
+        print(json.dumps(bench_modulate(torch.device("cuda", 0), args.modulate_only, w["hq"] * 128, w["n_chunks"], load_peaks())), flush=True)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -3,10 +3,11 @@
 // fp32 upcast, LayerNorm over the 128 channels with weight gamma+1 and bias (:355-357), non-interleaved
 // rotary on the first 2*rot_pairs channels in fp32, one rounding to bf16 at the end.
 //
-// Main kernel (prologue16_kernel): a HALF-warp owns one (token, head) row, 8 channels per lane with both channels of a
-// rotary pair in the same lane, so a warp instruction serves two rows and the rotation needs no shuffle; row index
-// arithmetic is 32-bit.  The generic kernel (4 channels per lane, one row per warp) covers source-blocked inputs,
-// rows that are only 8-byte aligned and the plain strided copy.
+// Main kernels: a QUARTER-warp (prologue8_kernel, rot_pairs % 8 == 0: the reference's 48) or a HALF-warp
+// (prologue16_kernel, any rot_pairs % 4 == 0) owns one (token, head) row, 16 or 8 channels per lane with both channels
+// of a rotary pair in the same lane, so a warp instruction serves four or two rows and the rotation needs no shuffle;
+// row index arithmetic is 32-bit.  The generic kernel (4 channels per lane, one row per warp) covers source-blocked
+// inputs, rows that are only 8-byte aligned and the plain strided copy.
 #include <cuda_bf16.h>
 
 #include <initializer_list>
@@ -128,7 +129,13 @@ __global__ void __launch_bounds__(256) prologue_kernel(PrologueKernelParams p) {
   }
 }
 
-constexpr int kRows16PerIter = 4;  // rows (heads) per half-warp in flight: 1 KB of loads per half-warp
+#ifndef MAGI_PRO_ROWS
+#define MAGI_PRO_ROWS 4
+#endif
+#ifndef MAGI_PRO_MINB
+#define MAGI_PRO_MINB 3
+#endif
+constexpr int kRows16PerIter = MAGI_PRO_ROWS;  // rows (heads) per half-warp in flight: 256 B of loads each
 
 // Main kernel.  A half-warp owns one (token, head) row of 128 channels, 8 per lane, laid out so that a rotary pair
 // (c, c + rot_pairs) lives in ONE thread: lane l < rot_pairs/4 holds channels 4l..4l+3 and rot_pairs+4l..rot_pairs+4l+3,
@@ -138,7 +145,7 @@ constexpr int kRows16PerIter = 4;  // rows (heads) per half-warp in flight: 1 KB
 // in fp32, far inside the bf16 rounding of the result), and the normalisation runs as packed fp32 pairs.
 // Work unit of a half-warp: one token x `hg` consecutive heads (hg divides H).  cos/sin of the token are loaded once per
 // unit and reused for its heads; the heads of a token are contiguous rows, so a unit streams hg * 256 contiguous bytes.
-__global__ void __launch_bounds__(256, 3) prologue16_kernel(PrologueKernelParams p, int hg) {
+__global__ void __launch_bounds__(256, MAGI_PRO_MINB) prologue16_kernel(PrologueKernelParams p, int hg) {
   using namespace ptx;
   const int lane = threadIdx.x & 31;
   const int l16 = lane & 15;
@@ -234,6 +241,133 @@ __global__ void __launch_bounds__(256, 3) prologue16_kernel(PrologueKernelParams
   }
 }
 
+#ifndef MAGI_PRO8_ROWS
+#define MAGI_PRO8_ROWS 4
+#endif
+#ifndef MAGI_PRO8_MINB
+#define MAGI_PRO8_MINB 2
+#endif
+constexpr int kRows8PerIter = MAGI_PRO8_ROWS;  // rows (heads) per quarter-warp in flight: 256 B of loads each
+
+// Quarter-warp form for rot_pairs % 8 == 0 (the reference's 48): EIGHT lanes own one (token, head) row, 16 channels per
+// lane, so a warp instruction serves four rows.  Lane l < rot_pairs/8 holds channels 8l..8l+7 and their rotary partners
+// rot_pairs+8l..rot_pairs+8l+7 (two 16-byte pieces); the remaining lanes hold 16 consecutive pass-through channels each.
+// Against the half-warp form this halves the loads, stores and address arithmetic per element and brings the two
+// reductions down from 8 to 6 shuffles per 16 (instead of 8) channels: the kernel is issue-bound once the SM clock
+// drops under the power cap, which is the state it runs in right after an attention kernel.
+__global__ void __launch_bounds__(256, MAGI_PRO8_MINB) prologue8_kernel(PrologueKernelParams p, int hg) {
+  using namespace ptx;
+  const int lane = threadIdx.x & 31;
+  const int l8 = lane & 7;
+  const unsigned qw_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;  // quarter-warp id
+  const unsigned n_qw = (gridDim.x * blockDim.x) >> 3;
+  const unsigned groups = (unsigned)p.H / (unsigned)hg;
+  const unsigned n_units = (unsigned)p.T * groups;
+  const int rp8 = p.rot_pairs >> 3;
+  const bool rot = l8 < rp8;
+  const int c0 = rot ? 8 * l8 : 2 * p.rot_pairs + 16 * (l8 - rp8);  // first eight channels of this lane
+  const int c1 = rot ? p.rot_pairs + 8 * l8 : c0 + 8;               // second eight (the rotary partners)
+
+  uint64_t g2[8], b2[8];  // (gamma + 1, beta) as packed pairs: [0..3] = channels c0.., [4..7] = channels c1..
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int c = half ? c1 : c0;
+    const float4 ga = *reinterpret_cast<const float4*>(p.gamma + c), gb = *reinterpret_cast<const float4*>(p.gamma + c + 4);
+    g2[4 * half + 0] = f2_pack(ga.x + 1.f, ga.y + 1.f); g2[4 * half + 1] = f2_pack(ga.z + 1.f, ga.w + 1.f);
+    g2[4 * half + 2] = f2_pack(gb.x + 1.f, gb.y + 1.f); g2[4 * half + 3] = f2_pack(gb.z + 1.f, gb.w + 1.f);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) b2[4 * half + k] = f2_pack(0.f, 0.f);
+    if (p.beta && p.norm_mode == MAGI_NORM_LAYERNORM_1P) {
+      const float4 ba = *reinterpret_cast<const float4*>(p.beta + c), bb = *reinterpret_cast<const float4*>(p.beta + c + 4);
+      b2[4 * half + 0] = f2_pack(ba.x, ba.y); b2[4 * half + 1] = f2_pack(ba.z, ba.w);
+      b2[4 * half + 2] = f2_pack(bb.x, bb.y); b2[4 * half + 3] = f2_pack(bb.z, bb.w);
+    }
+  }
+  const bool layernorm = p.norm_mode == MAGI_NORM_LAYERNORM_1P;
+  const unsigned hpb = (unsigned)p.heads_per_block;
+
+  // all four quarter-warps of a warp run the same number of iterations (shuffles are warp-wide)
+  const unsigned n_units_pad = (n_units + 3u) & ~3u;
+  for (unsigned unit = qw_global; unit < n_units_pad; unit += n_qw) {
+    const bool unit_live = unit < n_units;
+    const unsigned uc = unit_live ? unit : 0u;
+    const unsigned t = uc / groups;
+    const unsigned h0 = (uc - t * groups) * (unsigned)hg;
+    uint64_t cs2[4], sn2[4];  // cos, sin of this lane's 8 rotary pairs, packed
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { cs2[k] = f2_pack(1.f, 1.f); sn2[k] = f2_pack(0.f, 0.f); }
+    if (rot) {
+      const float4* cp = reinterpret_cast<const float4*>(p.cos + (int64_t)t * p.rot_pairs + 8 * l8);
+      const float4* sp = reinterpret_cast<const float4*>(p.sin + (int64_t)t * p.rot_pairs + 8 * l8);
+      const float4 ca = __ldg(cp), cb = __ldg(cp + 1), sa = __ldg(sp), sb = __ldg(sp + 1);
+      cs2[0] = f2_pack(ca.x, ca.y); cs2[1] = f2_pack(ca.z, ca.w); cs2[2] = f2_pack(cb.x, cb.y); cs2[3] = f2_pack(cb.z, cb.w);
+      sn2[0] = f2_pack(sa.x, sa.y); sn2[1] = f2_pack(sa.z, sa.w); sn2[2] = f2_pack(sb.x, sb.y); sn2[3] = f2_pack(sb.z, sb.w);
+    }
+    const __nv_bfloat16* xrow = p.x + (int64_t)t * p.x_stride_t;
+    for (int hb = 0; hb < hg; hb += kRows8PerIter) {
+      uint4 ra[kRows8PerIter], rb[kRows8PerIter];
+#pragma unroll
+      for (int i = 0; i < kRows8PerIter; ++i) {
+        const __nv_bfloat16* xr = xrow + (int64_t)(h0 + min(hb + i, hg - 1)) * p.x_stride_h;
+        ra[i] = __ldg(reinterpret_cast<const uint4*>(xr + c0));
+        rb[i] = __ldg(reinterpret_cast<const uint4*>(xr + c1));
+      }
+#pragma unroll
+      for (int i = 0; i < kRows8PerIter; ++i) {
+        const uint32_t w[8] = {ra[i].x, ra[i].y, ra[i].z, ra[i].w, rb[i].x, rb[i].y, rb[i].z, rb[i].w};
+        uint64_t v2[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v2[k] = f2_pack(__uint_as_float(w[k] << 16), __uint_as_float(w[k] & 0xffff0000u));
+        uint64_t s2 = f2_add(f2_add(f2_add(v2[0], v2[1]), f2_add(v2[2], v2[3])), f2_add(f2_add(v2[4], v2[5]), f2_add(v2[6], v2[7])));
+        uint64_t q2 = f2_pack(0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) q2 = f2_fma(v2[k], v2[k], q2);
+        float s_lo, s_hi, q_lo, q_hi;
+        f2_unpack(s2, s_lo, s_hi);
+        f2_unpack(q2, q_lo, q_hi);
+        float sum = s_lo + s_hi, sq = q_lo + q_hi;
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) {
+          sum += __shfl_xor_sync(0xffffffffu, sum, off);
+          sq += __shfl_xor_sync(0xffffffffu, sq, off);
+        }
+        const float mean = layernorm ? sum * (1.f / kHeadDim) : 0.f;
+        const float var = fmaxf(sq * (1.f / kHeadDim) - mean * mean, 0.f);
+        const float rstd = rsqrtf(var + p.eps);
+        const uint64_t r2 = f2_pack(rstd, rstd), m2 = f2_pack(-mean * rstd, -mean * rstd);
+        uint64_t y2[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) y2[k] = f2_fma(f2_fma(v2[k], r2, m2), g2[k], b2[k]);
+        if (rot) {  // out1 = x1 cos - x2 sin, out2 = x2 cos + x1 sin  (x1 = y2[0..3], x2 = y2[4..7])
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t x1 = y2[k], x2 = y2[4 + k];
+            const uint64_t nsn = sn2[k] ^ 0x8000000080000000ull;  // -sin, both lanes
+            y2[k] = f2_fma(x2, nsn, f2_fma(x1, cs2[k], f2_pack(0.f, 0.f)));
+            y2[4 + k] = f2_fma(x1, sn2[k], f2_fma(x2, cs2[k], f2_pack(0.f, 0.f)));
+          }
+        }
+        if (unit_live && hb + i < hg) {
+          const unsigned h = h0 + hb + i;
+          const unsigned blk = hpb > 0 ? h / hpb : 0u;
+          const unsigned hs = hpb > 0 ? h - blk * hpb : h;
+          __nv_bfloat16* ob = p.use_block_ptrs ? p.out_blocks[blk] : p.out + (int64_t)blk * p.out_stride_block;
+          __nv_bfloat16* orow = ob + (int64_t)t * p.out_stride_t + (int64_t)hs * p.out_stride_h;
+          uint32_t o[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            float lo, hi;
+            f2_unpack(y2[k], lo, hi);
+            o[k] = pack_bf16x2(lo, hi);
+          }
+          *reinterpret_cast<uint4*>(orow + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(orow + c1) = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+      }
+    }
+  }
+}
+
 static int check_prologue(magi_ctx* ctx, const magi_prologue_params* p, bool norm_rope) {
   if (!ctx) return MAGI_E_BADARG;
   if (!p || p->struct_size != sizeof(magi_prologue_params)) return set_err(ctx, MAGI_E_BADARG, "prologue: bad struct_size");
@@ -307,8 +441,14 @@ static int launch_prologue(magi_ctx* ctx, const magi_prologue_params* p, bool no
       if (p->H % cand == 0) { hg = cand; break; }
     const int64_t units = rows / hg;
     const int64_t want16 = (units + 15) / 16;  // 16 half-warps per block
-    const int64_t cap16 = (int64_t)ctx->sm_count * 4 * 4;  // 4 resident blocks per SM, x4 waves for balance
-    prologue16_kernel<<<(int)(want16 < cap16 ? want16 : cap16), 256, 0, stream>>>(k, hg);
+    const int64_t cap16 = (int64_t)ctx->sm_count * MAGI_PRO_MINB * 4;  // resident blocks per SM, x4 waves for balance
+    if ((p->rot_pairs & 7) == 0) {  // eight lanes per row
+      const int64_t want8 = (units + 31) / 32;  // 32 quarter-warps per block
+      const int64_t cap8 = (int64_t)ctx->sm_count * MAGI_PRO8_MINB * 4;
+      prologue8_kernel<<<(int)(want8 < cap8 ? want8 : cap8), 256, 0, stream>>>(k, hg);
+    } else {
+      prologue16_kernel<<<(int)(want16 < cap16 ? want16 : cap16), 256, 0, stream>>>(k, hg);
+    }
   } else if (norm_rope) {
     prologue_kernel<true><<<blocks, 256, 0, stream>>>(k);
   } else {
