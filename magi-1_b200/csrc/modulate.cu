@@ -78,6 +78,19 @@ __global__ void __launch_bounds__(kModThreads) modulate_kernel(ModulateKernelPar
     }
     float v[kModMaxVec][8];
     float sum = 0.f;
+    // a bf16 residual is fetched together with x (12 more registers) so that the row pays one DRAM latency, not two
+    uint4 res_raw[kModMaxVec];
+    if constexpr (!kResF32) {
+      if (p.residual) {
+#pragma unroll
+        for (int i = 0; i < kModMaxVec; ++i) {
+          const int vec = threadIdx.x + i * kModThreads;
+          if (vec < n_vec)
+            res_raw[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.residual) +
+                                                             (int64_t)row * p.res_stride + vec * 8));
+        }
+      }
+    }
 #pragma unroll
     for (int i = 0; i < kModMaxVec; ++i) {
       const int vec = threadIdx.x + i * kModThreads;
@@ -126,7 +139,16 @@ __global__ void __launch_bounds__(kModThreads) modulate_kernel(ModulateKernelPar
       if (vec < n_vec) {
         if (p.residual) {
           float r[8];
-          load8<kResF32>(p.residual, (int64_t)row * p.res_stride + vec * 8, r);
+          if constexpr (kResF32) {
+            load8<true>(p.residual, (int64_t)row * p.res_stride + vec * 8, r);
+          } else {
+            const uint32_t w[4] = {res_raw[i].x, res_raw[i].y, res_raw[i].z, res_raw[i].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              r[2 * k] = __uint_as_float(w[k] << 16);
+              r[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+            }
+          }
 #pragma unroll
           for (int k = 0; k < 8; ++k) v[i][k] += r[k];
         }
@@ -189,7 +211,7 @@ extern "C" int magi_bias_modulate_add(magi_ctx* ctx, const magi_modulate_params*
   k.gamma_plus_one = p->gamma_plus_one;
   k.eps = p->eps;
   k.status = reinterpret_cast<int*>(reinterpret_cast<char*>(ctx->workspace) + offsetof(PlanHeader, status));
-  const int64_t cap = (int64_t)ctx->sm_count * 8;  // 8 resident blocks of 256 threads per SM
+  const int64_t cap = (int64_t)ctx->sm_count * 12;  // 3-4 resident blocks of 256 threads per SM, a few waves for balance
   const int blocks = (int)(p->rows < cap ? p->rows : cap);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int prev = 0;
