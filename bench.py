@@ -88,6 +88,23 @@ def load_peaks():
         return dict(bf16_burst=1590.0, bf16_sustained=1400.0, hbm=6650.0, src="fallback")
 
 
+def bind_to_gpu_cpus(index):
+    """Run this rank on the CPUs NVML reports as local to its GPU (read-only query), so that the pinned host buffers of
+    the end-to-end leg are first touched - and therefore placed - on the GPU's own NUMA node.  Silently a no-op where the
+    query or the affinity call is not available or the mask would be empty."""
+    try:
+        import pynvml as nv
+        nv.nvmlInit()
+        h = nv.nvmlDeviceGetHandleByIndex(index)
+        words = nv.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64 + 16)
+        cpus = {64 * i + b for i, wd in enumerate(words) for b in range(64) if (wd >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+    except Exception:
+        pass
+
+
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
 
@@ -687,6 +704,7 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     torch.cuda.set_device(local_rank)
+    bind_to_gpu_cpus(local_rank)
     dist = None
     if world > 1:
         import torch.distributed as dist
