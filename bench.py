@@ -568,7 +568,16 @@ def run_ours(args, wname, rank, world, local_rank, steps, warmup, want_e2e, want
             threads = os.cpu_count() or 1
             cpu_attention_sample(w, 16, threads)
             f, t = cpu_attention_sample(w, CPU_SAMPLE_ROWS, threads)
-            cpu_b = {"value": f / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port", "seconds": t,
+            # BASELINE config 0 (the CPU-runnable case: 3 chunks x 128 tokens, 8/2 heads, fp32) timed in full
+            from oracle import chunk_attn_oracle as O
+            q0, k0, v0 = O.make_qkv(0, 384, 8, 2, scale=1.0 / math.sqrt(128))
+            qr0, kr0 = O.consecutive_q_ranges(3, 128), O.default_k_ranges(3, 128)
+            O.range_attention(q0, k0, v0, qr0, [[list(r)] for r in kr0])
+            t_c0 = time.perf_counter()
+            for _ in range(20):
+                O.range_attention(q0, k0, v0, qr0, [[list(r)] for r in kr0])
+            cfg0_ms = (time.perf_counter() - t_c0) / 20 * 1e3
+            cpu_b = {"value": f / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port", "seconds": t, "cfg0_full_ms": cfg0_ms,
                      "sample": f"1 of {Hkv} KV-head groups, {CPU_SAMPLE_ROWS} q rows of each of the {n} chunk ranges vs their full key ranges, fp32 eager torch"}
         per_gpu_flops = flops / cp
         achieved = per_gpu_flops / (attn_ms * 1e-3) / 1e12
@@ -620,6 +629,33 @@ def bench_modulate(dev, rows, hidden, n_gates, peaks):
     return {"kernel": "modulate_kernel", "bound": "hbm", "rows": rows, "hidden": hidden, "ms": ms, "algorithmic_bytes": nbytes,
             "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "peak_gbs": peaks["hbm"], "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm"],
             "max_abs_vs_torch_fp32_on_3_rows": err, "l2": "4.2 GB per launch, far beyond the 126 MB L2"}
+
+
+def bench_div_clamp(dev, rows, hidden, peaks):
+    """The FP8 linears' activation quantiser (div_clamp_to, dit_module.py:364-384) on the layer input at the workload's
+    token count: HBM-bound, bf16 read once, e4m3 written once."""
+    import magi_b200 as mb
+    g = torch.Generator(device=dev).manual_seed(10)
+    x = (torch.randn(rows, hidden, generator=g, device=dev) * 3).to(torch.bfloat16)
+    scale = torch.rand(hidden, generator=g, device=dev) * 0.05 + 0.01
+    out = torch.empty(rows, hidden, dtype=torch.float8_e4m3fn, device=dev)
+    for _ in range(3):
+        mb.div_clamp_to(x, scale, out=out)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(5):
+        mb.div_clamp_to(x, scale, out=out)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 5
+    nbytes = rows * hidden * 3
+    idx = torch.tensor([0, rows // 2, rows - 1], device=dev)
+    ref = torch.clamp(x[idx].float() / scale, -448, 448).bfloat16().to(torch.float8_e4m3fn)
+    same = bool(torch.equal(out[idx].view(torch.uint8), ref.view(torch.uint8)))
+    return {"kernel": "div_clamp_e4m3_kernel", "bound": "hbm", "rows": rows, "hidden": hidden, "ms": ms, "algorithmic_bytes": nbytes,
+            "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "peak_gbs": peaks["hbm"], "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm"],
+            "bytes_equal_torch_on_3_rows": same}
 
 
 def flash_child(wname):
@@ -753,6 +789,8 @@ def main():
         C_ = w["H"] * w["W"] * w["frames_per_chunk"]
         line["post_attention_modulate"] = bench_modulate(torch.device("cuda", local_rank), w["n_chunks"] * C_, w["hq"] * 128,
                                                          w["n_chunks"], load_peaks())
+        torch.cuda.empty_cache()
+        line["fp8_linear_quantiser"] = bench_div_clamp(torch.device("cuda", local_rank), w["n_chunks"] * C_, w["hq"] * 128, load_peaks())
         torch.cuda.empty_cache()
 
     # ---- 1-GPU default run only: the other BASELINE configurations, a few steps each, and the reference's fallback

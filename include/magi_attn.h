@@ -285,6 +285,15 @@ typedef struct {
 } magi_modulate_params;
 MAGI_API int magi_bias_modulate_add(magi_ctx* ctx, const magi_modulate_params* p, void* stream);
 
+/* Activation quantiser of the FP8 linear layers.  Replaces div_clamp_to (inference/model/dit/dit_module.py:364-384) as
+ * called by PerTensorQuantizedFp8Linear.forward (:449-461) and PerChannelQuantizedFp8Linear.forward (:484-495):
+ *     out = e4m3( bf16( clamp( float(x) / scale, -448, 448 ) ) )       x bf16 [rows, cols], out e4m3 [rows, cols]
+ * with `scale` fp32 [cols] (one per input channel) or, with scale_is_scalar, a single fp32.  Both roundings of the
+ * reference (to bf16, then to e4m3) are reproduced, so the bytes equal the reference's.  Strides in elements; cols a
+ * multiple of 8.  The GEMM that follows in the reference (bmm_fp8) is a library GEMM and is not part of this library. */
+MAGI_API int magi_div_clamp_to_e4m3(magi_ctx* ctx, const void* x, int64_t x_stride, int rows, int cols, const float* scale,
+                                    int scale_is_scalar, void* out, int64_t out_stride, void* stream);
+
 /* Peer-visible device buffers for the fused Ulysses exchange: cudaMalloc + CUDA IPC (plain peer loads / stores over
  * NVLink; no multicast object is created).  magi_peer_alloc returns the local pointer and a 64-byte handle to hand to
  * the other ranks of the box (e.g. through torch.distributed all_gather_object); magi_peer_open maps a peer's handle.

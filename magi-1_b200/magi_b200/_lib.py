@@ -19,7 +19,7 @@ EXPORTS = [
     "magi_kv_cache_append", "magi_kv_cache_evict", "magi_kv_cache_read", "magi_kv_cache_bytes",
     "magi_chunk_attn_fwd", "magi_chunk_attn_fwd_simt", "magi_quantize_e4m3_block128", "magi_chunk_attn_fwd_noalloc",
     "magi_peer_alloc", "magi_peer_open", "magi_peer_close", "magi_peer_free", "magi_selftest_bounded_wait",
-    "magi_bias_modulate_add",
+    "magi_bias_modulate_add", "magi_div_clamp_to_e4m3",
     "magi_ulysses_unique_id", "magi_ulysses_create", "magi_ulysses_destroy", "magi_ulysses_a2a_in", "magi_ulysses_a2a_out",
 ]
 
@@ -111,6 +111,7 @@ def _load():
         "magi_quantize_e4m3_block128": (C.c_int, [vp, vp, i64, i64, i32, i32, i32, vp, vp, vp, vp]),
         "magi_chunk_attn_fwd_noalloc": (C.c_int, [C.POINTER(AttnParams), vp, vp, C.c_char_p, i32]),
         "magi_bias_modulate_add": (C.c_int, [vp, C.POINTER(ModulateParams), vp]),
+        "magi_div_clamp_to_e4m3": (C.c_int, [vp, vp, i64, i32, i32, vp, i32, vp, i64, vp]),
         "magi_peer_alloc": (C.c_int, [vp, C.c_uint64, C.POINTER(vp), C.c_char_p]),
         "magi_peer_open": (C.c_int, [vp, C.c_char_p, C.POINTER(vp)]),
         "magi_peer_close": (C.c_int, [vp, vp]),

@@ -178,6 +178,59 @@ def bias_modulate_add(x: torch.Tensor, residual: torch.Tensor, condition_map: to
     return ops.bias_modulate_add(x, residual, condition_map, gate, post_norm)
 
 
+def div_clamp_to(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """Same name and arguments as the reference's div_clamp_to (inference/model/dit/dit_module.py:364-384)."""
+    return ops.div_clamp_to(x, scale)
+
+
+class PerTensorQuantizedFp8Linear:
+    """The reference's PerTensorQuantizedFp8Linear.forward (inference/model/dit/dit_module.py:431-461): the input is
+    divided by the per-input-channel `input_scale`, clamped and cast to e4m3 (one kernel here), then multiplied with the
+    e4m3 weight [out_features, in_features] by a library FP8 GEMM with fp32 accumulation and rescaled.  The reference hands
+    `input_scale` (a vector of in_features entries) and `weight_scale` (one entry) to flashinfer's bmm_fp8 as its two
+    per-tensor scales; bmm_fp8 applies them as scalars, and so does this class, taking the first entry of each.  The GEMM is
+    cuBLASLt through torch._scaled_mm: a plain library GEMM, outside the hand-written path."""
+
+    def __init__(self, weight: torch.Tensor, weight_scale: torch.Tensor, input_scale: torch.Tensor, dtype=torch.bfloat16):
+        if weight.dim() == 3:
+            weight = weight[0]
+        if weight.dtype != torch.float8_e4m3fn or weight.dim() != 2:
+            raise ValueError("weight must be float8_e4m3fn [out_features, in_features] (or [1, out, in])")
+        self.out_features, self.in_features = weight.shape
+        self.weight = weight.contiguous()
+        self.weight_scale = weight_scale.detach().float().reshape(-1)
+        self.input_scale = input_scale.detach().float().reshape(-1)
+        self.output_dtype = dtype
+
+    def _divisor(self) -> torch.Tensor:
+        return self.input_scale
+
+    def _gemm_scales(self):
+        return self.input_scale[:1], self.weight_scale[:1]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x8 = ops.div_clamp_to(x, self._divisor())
+        a_scale, b_scale = self._gemm_scales()
+        a = x8.reshape(-1, self.in_features)
+        y = torch._scaled_mm(a, self.weight.t(), scale_a=a_scale.to(a.device).reshape(()), scale_b=b_scale.to(a.device).reshape(()),
+                             out_dtype=self.output_dtype)
+        return y.reshape(x.shape[:-1] + (self.out_features,))
+
+    __call__ = forward
+
+
+class PerChannelQuantizedFp8Linear(PerTensorQuantizedFp8Linear):
+    """The reference's PerChannelQuantizedFp8Linear.forward (dit_module.py:466-495): the divisor is the per-input-channel
+    `smooth_scale` [1, in_features]; the GEMM's input scale is the one-entry `input_scale`."""
+
+    def __init__(self, weight, weight_scale, input_scale, smooth_scale, dtype=torch.bfloat16):
+        super().__init__(weight, weight_scale, input_scale, dtype)
+        self.smooth_scale = smooth_scale.detach().float().reshape(-1)
+
+    def _divisor(self) -> torch.Tensor:
+        return self.smooth_scale
+
+
 class ChunkCausalSelfAttention:
     """One layer's self-attention core: prologue -> KV-cache gate -> chunk-causal attention."""
 

@@ -421,6 +421,31 @@ def bias_modulate_add(x: torch.Tensor, residual: Optional[torch.Tensor], conditi
     return out.view(shape) if len(shape) == 3 else out
 
 
+def div_clamp_to(x: torch.Tensor, scale: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """e4m3(bf16(clamp(x.float() / scale.float(), -448, 448))): the reference's div_clamp_to
+    (inference/model/dit/dit_module.py:364-384) in one kernel, byte-identical.  x bf16 [..., cols] (contiguous last dim,
+    uniform row stride), scale fp32 with cols entries (per input channel) or one entry; returns float8_e4m3fn in x's shape."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or x.stride(-1) != 1:
+        raise ValueError("x must be a CUDA bf16 tensor with a contiguous last dim")
+    cols = x.shape[-1]
+    x2 = x.reshape(-1, cols)          # a view whenever the leading dims collapse; a copy otherwise
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    scale = scale.detach().to(device=x.device, dtype=torch.float32).reshape(-1).contiguous()
+    if scale.numel() not in (1, cols):
+        raise ValueError("scale must have one entry or one per channel of the last dimension")
+    ctx = Context.get(x.device)
+    if out is None:
+        out = torch.empty(rows, cols, dtype=torch.float8_e4m3fn, device=x.device)
+    elif out.dtype != torch.float8_e4m3fn or out.numel() != rows * cols or not out.is_contiguous():
+        raise ValueError("out must be a contiguous float8_e4m3fn tensor of x's size")
+    check(lib.magi_div_clamp_to_e4m3(ctx.handle, x2.data_ptr(), x2.stride(0) if rows > 1 else cols, rows, cols, scale.data_ptr(),
+                                     int(scale.numel() == 1), out.data_ptr(), cols, _stream(stream)), ctx.handle)
+    KERNEL_LAUNCHES[0] += 1
+    return out.view(x.shape)
+
+
 class PeerBuffer:
     """A device buffer other ranks of the box can map (CUDA IPC; plain peer loads / stores over NVLink, no multicast)."""
 

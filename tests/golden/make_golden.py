@@ -29,6 +29,9 @@ What is produced (all seeded, small enough to commit):
                  kernel inside it replaced by the one-line torch statement of what it computes (y[row] = x[row] *
                  gate[map[row]]: Triton needs a GPU), for an fp32 and a bf16 projection output.
 
+  div_clamp.npz  the reference's div_clamp_to (dit_module.py:364-384) on bf16 activations with a per-channel and a
+                 scalar scale: values around and beyond the e4m3 range, subnormal results, exact ties of both roundings.
+
 The reference holds no attention fixture of its own; see the oracle's header.
 """
 import argparse
@@ -337,6 +340,22 @@ def gen_modulate(ref_mod, out_dir):
     np.savez_compressed(os.path.join(out_dir, "modulate.npz"), **out)
 
 
+def gen_div_clamp(ref_mod, out_dir):
+    g = torch.Generator().manual_seed(53)
+    rows, cols = 48, 256
+    x = (torch.randn(rows, cols, generator=g) * torch.logspace(-3, 3, cols)).to(torch.bfloat16)
+    x[0, :16] = torch.tensor([0.0, -0.0, 448.0, -448.0, 464.0, 480.0, 1e30, -1e30, 2 ** -9, 2 ** -10, 3 * 2 ** -10, 2 ** -7,
+                              0.0625, 17.0, 18.0, 19.0]).to(torch.bfloat16)           # edges of e4m3, ties, saturation
+    scale_c = (torch.rand(cols, generator=g) * 3 + 0.05).float()
+    scale_c[:16] = 1.0
+    scale_s = torch.tensor([0.37])
+    out = {"x": bf16_bits(x), "scale_c": scale_c.numpy(), "scale_s": scale_s.numpy()}
+    with torch.no_grad():
+        out["out_c"] = ref_mod.div_clamp_to(x, scale_c).view(torch.uint8).numpy()
+        out["out_s"] = ref_mod.div_clamp_to(x.reshape(4, 12, cols), scale_s).view(torch.uint8).numpy()
+    np.savez_compressed(os.path.join(out_dir, "div_clamp.npz"), **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", required=True, help="root of the MAGI-1 checkout")
@@ -345,7 +364,7 @@ def main():
     a = ap.parse_args()
     sys.path.insert(0, a.ref)
     only = set(a.only.split(",")) if a.only else None
-    if only is None or "prologue" in only or "rope" in only or "modulate" in only:
+    if only is None or "prologue" in only or "rope" in only or "modulate" in only or "div_clamp" in only:
         import inference.model.dit.dit_module as ref_mod
         if only is None or "prologue" in only:
             gen_prologue(ref_mod, a.out)
@@ -353,6 +372,8 @@ def main():
             gen_rope(ref_mod, a.out)
         if only is None or "modulate" in only:
             gen_modulate(ref_mod, a.out)
+        if only is None or "div_clamp" in only:
+            gen_div_clamp(ref_mod, a.out)
     if only is None or "attn" in only:
         gen_attn_cfg0(a.out)
     if only is None or "ulysses" in only:

@@ -177,3 +177,26 @@ def test_eviction_horizon_bookkeeping_and_k_range_rebasing():
     import pytest
     with pytest.raises(ValueError):
         layer.core_attention(key, key, key, meta, cache, prefix)
+
+
+def test_flex_attn_accepts_the_reference_call_site():
+    """The drop-in seam: the keyword arguments with which FullyParallelAttention.core_attention calls the module
+    variable `flex_attention` (inference/model/dit/dit_module.py:1032-1043) must all be parameters of magi_b200.flex_attn,
+    and its positional arguments (q, k, v, q_range, k_range) must line up with flex_attn's leading parameters.  Read from
+    the reference's source text when the checkout is there."""
+    import ast
+    import inspect
+    import os
+    import pytest
+    path = "/root/reference/inference/model/dit/dit_module.py"
+    if not os.path.exists(path):
+        pytest.skip("reference checkout not present")
+    import magi_b200
+    calls = [n for n in ast.walk(ast.parse(open(path).read()))
+             if isinstance(n, ast.Call) and isinstance(n.func, ast.Name) and n.func.id == "flex_attention"]
+    assert calls, "no flex_attention call found in the reference"
+    params = list(inspect.signature(magi_b200.flex_attn).parameters)
+    for call in calls:
+        assert len(call.args) <= 5 and params[:5] == ["q", "k", "v", "q_ranges", "k_ranges"]
+        for kw in call.keywords:
+            assert kw.arg in params, f"flex_attn lacks the keyword {kw.arg} the reference passes"

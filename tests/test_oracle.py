@@ -139,3 +139,12 @@ def test_bias_modulate_add_matches_reference_fixture(golden_dir):
         diff = (got.float() - want.float()).abs()
         assert (diff <= want.float().abs() * 2 ** -7 + 1e-6).all(), f"{tag}: more than one bf16 ulp off ({diff.max().item()})"
         assert (got.view(torch.int16) == want.view(torch.int16)).float().mean().item() > 0.99
+
+
+def test_div_clamp_to_matches_reference_fixture(golden_dir):
+    """oracle.div_clamp_to against div_clamp.npz (the reference's own div_clamp_to): byte for byte."""
+    z = np.load(f"{golden_dir}/div_clamp.npz")
+    x = torch.from_numpy(z["x"].copy()).view(torch.bfloat16)
+    got_c = O.div_clamp_to(x, torch.from_numpy(z["scale_c"])).view(torch.uint8).numpy()
+    got_s = O.div_clamp_to(x.reshape(4, 12, -1), torch.from_numpy(z["scale_s"])).view(torch.uint8).numpy()
+    assert np.array_equal(got_c, z["out_c"]) and np.array_equal(got_s, z["out_s"])
