@@ -88,6 +88,16 @@ def load_peaks():
         return dict(bf16_burst=1590.0, bf16_sustained=1400.0, hbm=6650.0, src="fallback")
 
 
+def nvml_handle(nv, index):
+    """NVML handle of CUDA device `index` of this process: matched by PCI address, since NVML numbers the physical GPUs
+    while CUDA numbers the visible ones."""
+    try:
+        pr = torch.cuda.get_device_properties(index)
+        return nv.nvmlDeviceGetHandleByPciBusId(f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0")
+    except Exception:
+        return nv.nvmlDeviceGetHandleByIndex(index)
+
+
 def bind_to_gpu_cpus(index):
     """Run this rank on the CPUs NVML reports as local to its GPU (read-only query), so that the pinned host buffers of
     the end-to-end leg are first touched - and therefore placed - on the GPU's own NUMA node.  Silently a no-op where the
@@ -95,7 +105,7 @@ def bind_to_gpu_cpus(index):
     try:
         import pynvml as nv
         nv.nvmlInit()
-        h = nv.nvmlDeviceGetHandleByIndex(index)
+        h = nvml_handle(nv, index)
         words = nv.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64 + 16)
         cpus = {64 * i + b for i, wd in enumerate(words) for b in range(64) if (wd >> b) & 1}
         cpus &= os.sched_getaffinity(0)
@@ -116,7 +126,7 @@ class ClockSampler(threading.Thread):
         try:
             import pynvml as nv
             nv.nvmlInit()
-            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            h = nvml_handle(nv, self.index)
             self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
             names = {nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap", nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
                      nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
