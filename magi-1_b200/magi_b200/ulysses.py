@@ -164,8 +164,11 @@ class UlyssesAttention:
     def forward(self, xq, xk, xv, gq, bq, gk, bk, cos, sin, q_ranges, k_ranges, max_seqlen_q, max_seqlen_k,
                 eps: float = 1e-6, norm_mode: str = "layernorm_1p", cache=None, layer: int = 0,
                 prefix_chunk_ids: Sequence[int] = (), k_range_offsets=None, attn_events: Optional[list] = None,
-                fp8_chunk_tokens: int = 0, cross_attn_func=None):
+                fp8_chunk_tokens: int = 0, cross_attn_func=None, kv_current_offset: int = 0):
         """xq [s_local, Hq, 128], xk / xv [s_local, Hkv, 128]: this rank's tokens, all heads (projection outputs).
+        cache / prefix_chunk_ids: a head-sharded paged prefix (the cache holds this rank's Hkv/cp heads,
+        dit_module.py:794-798); kv_current_offset: the received K/V from this token on are the "current" keys, earlier
+        tokens are served by the prefix pages.
         cross_attn_func: optional callable run after the last head group's attention has been enqueued, while its output
         exchange is in flight (the cross-attention slot of the reference's schedule, context_parallel.py:591); forward
         then returns (O, cross_attn_func()).
@@ -188,7 +191,7 @@ class UlyssesAttention:
         ops.qk_norm_rope(xq, gq, bq, cos, sin, eps, norm_mode, out=q_send, heads_per_block=self.hq_loc)
         q_recv, w_q = ex.scatter_heads(q_send, self._buf("q_recv", (S, self.hq_loc, HEAD_DIM), dev))
         w_kv.wait()
-        k_full, v_full = kv_recv[..., :HEAD_DIM], kv_recv[..., HEAD_DIM:]
+        k_full, v_full = kv_recv[kv_current_offset:, :, :HEAD_DIM], kv_recv[kv_current_offset:, :, HEAD_DIM:]
         fp8 = {}
         if fp8_chunk_tokens > 0:
             k_full, ks = ops.quantize_e4m3(k_full, fp8_chunk_tokens)

@@ -181,6 +181,10 @@ def test_ulysses_attention_matches_oracle(world, overlap, head_order):
     _spawn(world, overlap=overlap, head_order=head_order)
 
 
+def test_ulysses_attention_with_a_head_sharded_paged_prefix():
+    _spawn(2, cache=True)
+
+
 def test_ulysses_attention_cross_attention_slot():
     _spawn(2, overlap=2, xattn=True)
 
