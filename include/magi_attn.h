@@ -40,7 +40,7 @@ enum {
 };
 
 enum { MAGI_DTYPE_BF16 = 0, MAGI_DTYPE_FP8_E4M3 = 1, MAGI_DTYPE_F32 = 2 };
-enum { MAGI_NORM_LAYERNORM_1P = 0, MAGI_NORM_RMSNORM_1P = 1 };
+enum { MAGI_NORM_LAYERNORM_1P = 0, MAGI_NORM_RMSNORM_1P = 1, MAGI_NORM_NONE = 2 /* magi_linear_qk_norm_rope_fwd only */ };
 
 typedef struct magi_ctx magi_ctx;
 typedef struct magi_kv_cache magi_kv_cache;
@@ -109,6 +109,39 @@ MAGI_API int magi_qk_norm_rope_fwd(magi_ctx* ctx, const magi_prologue_params* p,
  * FullyParallelAttention.get_v, inference/model/dit/dit_module.py:987-989, and the torch.cat of K and V at
  * :996).  x, out: bf16. */
 MAGI_API int magi_head_block_copy(magi_ctx* ctx, const magi_prologue_params* p, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Projection + prologue in one kernel: out = prologue( bf16( x @ w^T ) ), the prologue running in the GEMM's
+ * epilogue.  Replaces FullyParallelAttention.get_q / get_k / get_v including the linear they start with
+ * (inference/model/dit/dit_module.py:953-963 with linear_qkv.forward_q :415-416; :970-980 with forward_k
+ * :421-422; :987-989 with forward_v :424-425), for the bf16 torch.nn.Linear case of CustomLayerNormLinear
+ * (:406-408; the FP8 linears of the middle layers keep the separate quantiser + library GEMM + prologue).
+ * One call per projection.  norm_mode MAGI_NORM_NONE = plain linear (get_v): gamma, beta, cos, sin ignored.
+ * The linear's result is rounded to bf16 before the norm, as the reference's Linear output is, and never
+ * reaches HBM.  in_features must be a multiple of 128; rot_pairs one of 0, 32, 48, 64.  Destination
+ * addressing (blocks of heads, optional per-block base pointers, peer-mapped or not) as magi_prologue_params.
+ */
+typedef struct {
+  uint32_t struct_size;      /* sizeof(magi_linear_prologue_params) */
+  int32_t norm_mode;         /* MAGI_NORM_*                                                        */
+  const void* x;             /* bf16 [T, in_features], row stride x_stride elements (multiple of 8), 16-byte aligned */
+  int64_t x_stride;
+  const void* w;             /* bf16 [H * 128, in_features] = torch.nn.Linear.weight, row stride w_stride */
+  int64_t w_stride;
+  int32_t T, H, in_features;
+  float eps;
+  const float* gamma;        /* fp32 [128]; applied as gamma + 1                                   */
+  const float* beta;         /* fp32 [128] or NULL; ignored for RMSNORM                            */
+  int32_t rot_pairs;
+  int32_t heads_per_block;   /* 0 or >= H: no blocking */
+  const float* cos;          /* fp32 [T, rot_pairs], 16-byte aligned                               */
+  const float* sin;
+  void* out;                 /* bf16; element (t,h,d) at out + (h / heads_per_block)*out_stride_block
+                                + t*out_stride_t + (h % heads_per_block)*out_stride_h + d         */
+  int64_t out_stride_t, out_stride_h, out_stride_block;
+  void* const* out_block_ptrs; /* optional HOST array of H / heads_per_block device pointers (at most 16) */
+} magi_linear_prologue_params;
+MAGI_API int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_prologue_params* p, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------
  * Chunk-paged KV cache.  Replaces Attention._allocate_key_and_value_memory

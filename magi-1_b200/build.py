@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 BUILD = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "magi_b200", "libmagi_attn.so")
-SOURCES = ["api.cu", "plan.cu", "prologue.cu", "attn_simt.cu", "attn_fwd_sm100.cu", "attn_fwd_q1_sm100.cu", "attn_fwd_fp8_sm100.cu", "fp8.cu", "selftest.cu", "ulysses.cu", "modulate.cu", "quant_linear.cu"]
+SOURCES = ["api.cu", "plan.cu", "prologue.cu", "attn_simt.cu", "attn_fwd_sm100.cu", "attn_fwd_fp8_sm100.cu", "fp8.cu", "selftest.cu", "ulysses.cu", "modulate.cu", "quant_linear.cu", "linear_prologue_sm100.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

@@ -344,13 +344,9 @@ int make_tile_map(magi_ctx* ctx, CUtensorMap* m, const void* base, int64_t strid
 }
 
 int attn_fp8_init_device(magi_ctx* ctx);
-int attn_q1_init_device(magi_ctx* ctx);
-int launch_attn_bf16_q1(magi_ctx* ctx, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tkc,
-                        const CUtensorMap& tvc, const AttnKernelParams& kp, int max_items, int n_q_heads, cudaStream_t stream);
 // Opt in to > 48 KB of dynamic shared memory; called once per context with its device current.
 int attn_init_device(magi_ctx* ctx) {
   if (int rc = attn_fp8_init_device(ctx)) return rc;
-  if (int rc = attn_q1_init_device(ctx)) return rc;
   MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::kDynamic));
   MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::kDynamic));
   return MAGI_OK;
@@ -392,8 +388,6 @@ int launch_attn_bf16(magi_ctx* ctx, const magi_attn_params* p, int max_items, cu
   fill_peer_table(kp, p);
 
   dim3 grid(max_items, p->n_q_heads, 1);
-  const char* q1 = getenv("MAGI_ATTN_Q1");
-  if (q1 && q1[0] == '1') return launch_attn_bf16_q1(ctx, tq, tk, tv, tkc, tvc, kp, max_items, p->n_q_heads, stream);
   // MAGI_ATTN_SINGLE_ISSUER=1 selects the one-thread issuer (kept for A/B measurements; about 2 % slower)
   const char* v = getenv("MAGI_ATTN_SINGLE_ISSUER");
   if (v && v[0] == '1') attn_fwd_kernel<false><<<grid, kAttnThreads, SmemLayout::kDynamic, stream>>>(tq, tk, tv, tkc, tvc, kp);

@@ -1,0 +1,402 @@
+// Q / K / V projection with the per-head prologue in the GEMM's epilogue, for sm_100a.
+// Replaces, in one kernel per projection, FullyParallelAttention.get_q / get_k / get_v
+// (inference/model/dit/dit_module.py:953-963, :970-980, :987-989):
+//     y   = bf16( x @ W^T )                       linear_qkv.forward_q / forward_k / forward_v (:415-425), torch.nn.Linear, no bias
+//     out = bf16( rope( layer_norm_1p( float(y) ) ) )   per (token, head) over the 128 channels of the head; V: out = y
+// The reference writes y to HBM, reads it back as fp32, normalises, transposes, rotates, casts and rearranges.  Here a
+// head is exactly one 128-column block of the GEMM's N dimension, and a TMEM lane holds one token's accumulator row: the
+// thread that drains a lane has the whole head of that token in registers, so mean, variance, the rotary pair
+// (c, c + rot_pairs) and the cast need no exchange between threads at all, and y never exists in HBM.  The accumulator
+// is rounded to bf16 before the norm, as the reference's Linear rounds its output.
+//
+// GEMM: x [T, K] and W [H*128, K] are both K-major, so both operands come in by TMA (128-byte swizzle, 64 k-elements per
+// stage) and go to tcgen05.mma straight from shared memory.  CTA tile = (kMT x 128) tokens x 256 channels (two heads):
+// kMT = 2 uses all 512 TMEM columns for one tile and loads 64 KB per 8 UMMAs (64 B per cycle per SM from L2); kMT = 1
+// keeps two 256-column accumulators so that the epilogue of a tile overlaps the main loop of the next, at 96 B per cycle.
+//
+//   warp 0      TMA producer (one thread): A and B k-blocks into a ring of stages
+//   warp 1      UMMA issuer (one thread)
+//   warps 2-9   epilogue: warp w drains TMEM lane quarter w % 4; kMT = 2: warps 2-5 take one row tile, 6-9 the other, both
+//               heads each; kMT = 1: warps 2-5 take head 0 of the tile, 6-9 head 1
+// Persistent: CTA b takes tiles b, b + grid, ...; tiles are numbered with the channel block fastest, so the CTAs running
+// at any time share a few row blocks of x and all of W through L2.  Every wait is bounded (MAGI_E_TIMEOUT).
+#include <cuda_bf16.h>
+#include <math.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace magi {
+using namespace ptx;
+
+int make_tile_map(magi_ctx* ctx, CUtensorMap* m, const void* base, int64_t stride_t, int64_t stride_h, int tokens,
+                  int heads, int elem_bytes, const char* what);
+
+constexpr int kLpThreads = 320;
+constexpr int kLpKBlock = 64;                                  // k-elements per stage: one 128-byte swizzle row
+constexpr int kLpSlab = 128 * kLpKBlock * 2;                   // 128 rows x 128 bytes = 16 KB
+constexpr int kLpTileN = 256;                                  // two heads
+
+template <int kMT>
+struct SmemLp {
+  static constexpr int kStageBytes = (kMT + 2) * kLpSlab;      // A: kMT slabs, B: two slabs (256 channels)
+  static constexpr int kStages = kMT == 2 ? 3 : 4;             // 192 KB either way
+  static constexpr int kAccSets = 2 / kMT;                     // TMEM: kAccSets x kMT x 256 columns = 512
+  static constexpr int kRing = 0;
+  static constexpr int kStore = kStages * kStageBytes;         // 8 epilogue warps x 4 KB: 32 rows x 64 channels bf16
+  static constexpr int kBar = kStore + 8 * 4096;
+  static constexpr int kNumBars = 2 * kStages + 2 * kAccSets;  // full, empty, acc_full, acc_empty
+  static constexpr int kMisc = kBar + kNumBars * 8;            // tmem slot, abort flag
+  static constexpr int kGamma = kMisc + 16;                    // float (gamma + 1)[128], beta[128]
+  static constexpr int kTotal = kGamma + 1024;
+  static constexpr int kDynamic = kTotal + 1024;               // slack to align the base to 1024 bytes
+};
+static_assert(SmemLp<1>::kDynamic <= 232448 && SmemLp<2>::kDynamic <= 232448, "shared memory per CTA");
+
+struct LinearPrologueKernelParams {
+  int T, H, k_blocks;
+  int norm_mode;  // -1: plain linear
+  float eps;
+  const float* gamma;
+  const float* beta;
+  const float* cos;
+  const float* sin;
+  __nv_bfloat16* out;
+  int64_t out_stride_t, out_stride_h, out_stride_block;
+  int heads_per_block;  // 0: no blocking
+  int use_block_ptrs;
+  __nv_bfloat16* out_blocks[16];
+  int tiles_m, tiles_n;
+  int* status;
+};
+
+// One head of one token: 128 fp32 accumulators in registers -> bf16 rounding of the linear's output -> norm -> rotary
+// -> 64 packed bf16 pairs.  kRot = rotary pairs (channel c pairs with c + kRot, c < kRot), a compile-time constant so
+// that every register index is static.
+template <int kRot>
+__device__ __forceinline__ void head_epilogue(float (&v)[kHeadDim], uint32_t (&o)[kHeadDim / 2], const LinearPrologueKernelParams& p,
+                                              const float* g_sh, const float* b_sh, int64_t token, bool row_valid) {
+#pragma unroll
+  for (int c = 0; c < kHeadDim; ++c) v[c] = __bfloat162float(__float2bfloat16_rn(v[c]));
+  if (p.norm_mode >= 0) {
+    float rstd;
+    if (p.norm_mode == MAGI_NORM_LAYERNORM_1P) {
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+      for (int c = 0; c < kHeadDim; c += 4) { s0 += v[c]; s1 += v[c + 1]; s2 += v[c + 2]; s3 += v[c + 3]; }
+      const float mean = ((s0 + s1) + (s2 + s3)) * (1.f / kHeadDim);
+      s0 = s1 = s2 = s3 = 0.f;
+#pragma unroll
+      for (int c = 0; c < kHeadDim; c += 4) {
+        v[c] -= mean; v[c + 1] -= mean; v[c + 2] -= mean; v[c + 3] -= mean;
+        s0 = fmaf(v[c], v[c], s0); s1 = fmaf(v[c + 1], v[c + 1], s1); s2 = fmaf(v[c + 2], v[c + 2], s2); s3 = fmaf(v[c + 3], v[c + 3], s3);
+      }
+      rstd = rsqrtf(((s0 + s1) + (s2 + s3)) * (1.f / kHeadDim) + p.eps);
+#pragma unroll
+      for (int c = 0; c < kHeadDim; ++c) v[c] = v[c] * rstd * g_sh[c] + b_sh[c];  // same address in every lane: a broadcast
+    } else {
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+      for (int c = 0; c < kHeadDim; c += 4) {
+        s0 = fmaf(v[c], v[c], s0); s1 = fmaf(v[c + 1], v[c + 1], s1); s2 = fmaf(v[c + 2], v[c + 2], s2); s3 = fmaf(v[c + 3], v[c + 3], s3);
+      }
+      rstd = rsqrtf(((s0 + s1) + (s2 + s3)) * (1.f / kHeadDim) + p.eps);
+#pragma unroll
+      for (int c = 0; c < kHeadDim; ++c) v[c] = v[c] * rstd * g_sh[c];
+    }
+    if constexpr (kRot > 0) {
+      if (row_valid) {
+        const float4* cs = reinterpret_cast<const float4*>(p.cos + token * kRot);
+        const float4* sn = reinterpret_cast<const float4*>(p.sin + token * kRot);
+#pragma unroll
+        for (int c4 = 0; c4 < kRot / 4; ++c4) {
+          const float4 c = __ldg(cs + c4), s = __ldg(sn + c4);
+          const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float a = v[4 * c4 + i], b = v[4 * c4 + i + kRot];
+            v[4 * c4 + i] = a * cc[i] - b * ss[i];
+            v[4 * c4 + i + kRot] = b * cc[i] + a * ss[i];
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < kHeadDim / 2; ++c) o[c] = pack_bf16x2(v[2 * c], v[2 * c + 1]);
+}
+
+template <int kMT, int kRot>
+__global__ void __launch_bounds__(kLpThreads, 1)
+linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                       const LinearPrologueKernelParams p) {
+  using L = SmemLp<kMT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  uint64_t* full = bars;
+  uint64_t* empty = full + L::kStages;
+  uint64_t* acc_full = empty + L::kStages;
+  uint64_t* acc_empty = acc_full + L::kAccSets;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
+  float* g_sh = reinterpret_cast<float*>(smem + L::kGamma);
+  float* b_sh = g_sh + kHeadDim;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < L::kAccSets; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (threadIdx.x < kHeadDim) {
+    g_sh[threadIdx.x] = p.norm_mode >= 0 ? p.gamma[threadIdx.x] + 1.0f : 1.0f;
+    b_sh[threadIdx.x] = (p.norm_mode == MAGI_NORM_LAYERNORM_1P && p.beta) ? p.beta[threadIdx.x] : 0.0f;
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const int n_tiles = p.tiles_m * p.tiles_n;
+  uint8_t* ring = smem + L::kRing;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_x);
+      tma_prefetch_desc(&tm_w);
+      int fill = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int row0 = (tile / p.tiles_n) * (kMT * 128), ch0 = (tile % p.tiles_n) * kLpTileN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++fill) {
+          const int stage = fill % L::kStages, use = fill / L::kStages;
+          if (use > 0) ok = mbar_wait(&empty[stage], (use & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          uint8_t* dst = ring + stage * L::kStageBytes;
+          mbar_expect_tx(&full[stage], L::kStageBytes);
+          // x and W are seen as [rows, K / 128, 128]: k-block kb is the half (kb & 1) of 128-column group kb >> 1
+          const int c0 = (kb & 1) * kLpKBlock, c1 = kb >> 1;
+#pragma unroll
+          for (int m = 0; m < kMT; ++m) tma_load_3d(dst + m * kLpSlab, &tm_x, &full[stage], c0, c1, row0 + m * 128);
+          tma_load_3d(dst + kMT * kLpSlab, &tm_w, &full[stage], c0, c1, ch0);
+          tma_load_3d(dst + (kMT + 1) * kLpSlab, &tm_w, &full[stage], c0, c1, ch0 + 128);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(128, kLpTileN, 1, 1, 0, 0);
+      constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO = 1024 B, version 1, 128-byte swizzle
+      const uint32_t ring_lo = (smem_u32(ring) >> 4) | (1u << 16);         // K-major: LBO field = 1
+      int fill = 0, t_local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t_local) {
+        const int a = t_local % L::kAccSets, a_use = t_local / L::kAccSets;
+        if (a_use > 0) ok = mbar_wait(&acc_empty[a], (a_use & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t tD = tmem_base + a * (kMT * kLpTileN);
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++fill) {
+          const int stage = fill % L::kStages;
+          ok = mbar_wait(&full[stage], (uint32_t)(fill / L::kStages) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t s_lo = ring_lo + stage * (L::kStageBytes >> 4);
+          const uint32_t b_lo = s_lo + kMT * (kLpSlab >> 4);
+#pragma unroll
+          for (int m = 0; m < kMT; ++m) {
+            const uint32_t a_lo = s_lo + m * (kLpSlab >> 4);
+            const uint32_t d = tD + m * kLpTileN;
+            if (kb == 0) umma_ss_f16_lh<0>(d, a_lo, b_lo, desc_hi, idesc);
+            else umma_ss_f16_lh<1>(d, a_lo, b_lo, desc_hi, idesc);
+#pragma unroll
+            for (int k = 1; k < 4; ++k) umma_ss_f16_lh<1>(d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);  // 16 k-elements = 32 bytes
+          }
+          umma_commit(&empty[stage]);
+        }
+        if (ok) umma_commit(&acc_full[a]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    const int ew = warp - 2;                 // 0..7
+    const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
+    const int sel = ew >> 2;                 // kMT = 2: row tile; kMT = 1: head of the tile
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    uint8_t* stage_sh = smem + L::kStore + ew * 4096;
+    bool ok = true;
+    int t_local = 0;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t_local) {
+      const int a = t_local % L::kAccSets;
+      const int row0 = (tile / p.tiles_n) * (kMT * 128) + (kMT == 2 ? sel * 128 : 0) + quarter * 32;
+      const int head0 = (tile % p.tiles_n) * 2;
+      ok = mbar_wait(&acc_full[a], (uint32_t)(t_local / L::kAccSets) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t tD = tmem_base + lane_base + a * (kMT * kLpTileN) + (kMT == 2 ? sel * kLpTileN : 0);
+      const int64_t token = row0 + lane;
+      const bool row_valid = token < p.T;
+#pragma unroll 1
+      for (int hh = (kMT == 2 ? 0 : sel); hh < (kMT == 2 ? 2 : sel + 1); ++hh) {
+        const int head = head0 + hh;
+        float v[kHeadDim];
+        uint32_t o[kHeadDim / 2];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tD + hh * kHeadDim + c * 32, reinterpret_cast<uint32_t*>(v) + c * 32);
+        tmem_wait_ld();
+        if (hh == (kMT == 2 ? 1 : sel)) {  // the last read of this accumulator by this warp
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[a]);
+        }
+        if (head >= p.H) continue;  // warp-uniform: an odd head count leaves half of the last channel block empty
+        head_epilogue<kRot>(v, o, p, g_sh, b_sh, token, row_valid);
+        // destination of (token, head): block of heads, then the row inside it
+        const int blk = p.heads_per_block > 0 ? head / p.heads_per_block : 0;
+        const int hs = p.heads_per_block > 0 ? head - blk * p.heads_per_block : head;
+        __nv_bfloat16* base = (p.use_block_ptrs ? p.out_blocks[blk] : p.out + blk * p.out_stride_block) + hs * p.out_stride_h;
+        // staged through 4 KB of shared memory per warp, 64 channels at a time, so that the global stores are whole
+        // 128-byte pieces of a row (eight lanes per row, four rows per instruction); 16-byte chunks XOR-swizzled by row
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(stage_sh + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+                make_uint4(o[half * 32 + 4 * c], o[half * 32 + 4 * c + 1], o[half * 32 + 4 * c + 2], o[half * 32 + 4 * c + 3]);
+          __syncwarp();
+          const int l8 = lane & 7, rsel = lane >> 3;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = 4 * i + rsel;
+            if (row0 + rr < p.T) {
+              const uint4 val = *reinterpret_cast<const uint4*>(stage_sh + rr * 128 + ((l8 ^ (rr & 7)) << 4));
+              *reinterpret_cast<uint4*>(base + (int64_t)(row0 + rr) * p.out_stride_t + half * 64 + l8 * 8) = val;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0 && p.status) *p.status = MAGI_E_TIMEOUT;
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+template <int kMT, int kRot>
+static int launch_lp(magi_ctx* ctx, const CUtensorMap& tx, const CUtensorMap& tw, const LinearPrologueKernelParams& k, cudaStream_t st) {
+  static bool configured[64] = {};  // per device: opt in to > 48 KB of dynamic shared memory once
+  if (ctx->device < 64 && !configured[ctx->device]) {
+    MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(linear_prologue_kernel<kMT, kRot>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SmemLp<kMT>::kDynamic));
+    configured[ctx->device] = true;
+  }
+  const int n_tiles = k.tiles_m * k.tiles_n;
+  const int grid = n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count;
+  linear_prologue_kernel<kMT, kRot><<<grid, kLpThreads, SmemLp<kMT>::kDynamic, st>>>(tx, tw, k);
+  MAGI_CUDA_OK(ctx, cudaGetLastError());
+  return MAGI_OK;
+}
+
+template <int kMT>
+static int launch_lp_rot(magi_ctx* ctx, int rot, const CUtensorMap& tx, const CUtensorMap& tw, const LinearPrologueKernelParams& k,
+                         cudaStream_t st) {
+  switch (rot) {
+    case 0: return launch_lp<kMT, 0>(ctx, tx, tw, k, st);
+    case 32: return launch_lp<kMT, 32>(ctx, tx, tw, k, st);
+    case 48: return launch_lp<kMT, 48>(ctx, tx, tw, k, st);
+    case 64: return launch_lp<kMT, 64>(ctx, tx, tw, k, st);
+  }
+  return set_err(ctx, MAGI_E_BADARG, "linear prologue: rot_pairs must be 0, 32, 48 or 64 (the reference uses 48)");
+}
+
+}  // namespace magi
+
+extern "C" int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_prologue_params* p, void* stream) {
+  using namespace magi;
+  if (!ctx) return MAGI_E_BADARG;
+  if (!p || p->struct_size != sizeof(magi_linear_prologue_params)) return set_err(ctx, MAGI_E_BADARG, "linear prologue: bad struct_size");
+  if (!p->x || !p->w || (!p->out && !p->out_block_ptrs) || p->T < 0 || p->H <= 0 || p->in_features <= 0)
+    return set_err(ctx, MAGI_E_BADARG, "linear prologue: null tensor or bad shape");
+  if (p->in_features % 128) return set_err(ctx, MAGI_E_BADARG, "linear prologue: in_features must be a multiple of 128");
+  const bool plain = p->norm_mode == MAGI_NORM_NONE;
+  if (!plain && p->norm_mode != MAGI_NORM_LAYERNORM_1P && p->norm_mode != MAGI_NORM_RMSNORM_1P)
+    return set_err(ctx, MAGI_E_BADARG, "linear prologue: unknown norm_mode %d", p->norm_mode);
+  const int rot = plain ? 0 : p->rot_pairs;
+  if (!plain) {
+    if (!p->gamma) return set_err(ctx, MAGI_E_BADARG, "linear prologue: gamma is required");
+    if (rot > 0 && (!p->cos || !p->sin)) return set_err(ctx, MAGI_E_BADARG, "linear prologue: cos/sin required");
+    if (rot > 0 && ((reinterpret_cast<uintptr_t>(p->cos) & 15) || (reinterpret_cast<uintptr_t>(p->sin) & 15)))
+      return set_err(ctx, MAGI_E_ALIGN, "linear prologue: cos/sin must be 16-byte aligned");
+  }
+  if (p->out_block_ptrs) {
+    if (p->heads_per_block <= 0 || p->H % p->heads_per_block || p->H / p->heads_per_block > 16)
+      return set_err(ctx, MAGI_E_BADARG, "linear prologue: out_block_ptrs needs heads_per_block dividing H into at most 16 blocks");
+    for (int b = 0; b < p->H / p->heads_per_block; ++b)
+      if (!p->out_block_ptrs[b] || (reinterpret_cast<uintptr_t>(p->out_block_ptrs[b]) & 15))
+        return set_err(ctx, MAGI_E_ALIGN, "linear prologue: out_block_ptrs[%d] is null or not 16-byte aligned", b);
+  }
+  if ((reinterpret_cast<uintptr_t>(p->out) & 15) || (p->out_stride_t & 7) || (p->out_stride_h & 7) || (p->out_stride_block & 7))
+    return set_err(ctx, MAGI_E_ALIGN, "linear prologue: out must be 16-byte aligned and its strides multiples of 8 elements");
+  if (p->T == 0) return MAGI_OK;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  if (prev != ctx->device) cudaSetDevice(ctx->device);
+  CUtensorMap tx, tw;
+  int rc = make_tile_map(ctx, &tx, p->x, p->x_stride, 128, p->T, p->in_features / 128, 2, "linear prologue x");
+  if (!rc) rc = make_tile_map(ctx, &tw, p->w, p->w_stride, 128, p->H * kHeadDim, p->in_features / 128, 2, "linear prologue w");
+  if (!rc) {
+    LinearPrologueKernelParams k;
+    k.T = p->T;
+    k.H = p->H;
+    k.k_blocks = p->in_features / kLpKBlock;
+    k.norm_mode = plain ? -1 : p->norm_mode;
+    k.eps = p->eps;
+    k.gamma = p->gamma;
+    k.beta = p->beta;
+    k.cos = p->cos;
+    k.sin = p->sin;
+    k.out = reinterpret_cast<__nv_bfloat16*>(p->out);
+    k.out_stride_t = p->out_stride_t;
+    k.out_stride_h = p->out_stride_h;
+    k.out_stride_block = p->out_stride_block;
+    k.heads_per_block = (p->heads_per_block > 0 && (p->heads_per_block < p->H || p->out_block_ptrs)) ? p->heads_per_block : 0;
+    k.use_block_ptrs = p->out_block_ptrs ? 1 : 0;
+    for (int b = 0; b < 16; ++b)
+      k.out_blocks[b] = (p->out_block_ptrs && b < p->H / p->heads_per_block) ? reinterpret_cast<__nv_bfloat16*>(p->out_block_ptrs[b]) : nullptr;
+    k.tiles_n = (p->H + 1) / 2;
+    k.status = reinterpret_cast<int*>(reinterpret_cast<char*>(ctx->workspace) + offsetof(PlanHeader, status));
+    // 256-row tiles (less traffic from L2 per flop) unless the problem is too small to fill the SMs with them
+    const int64_t tiles256 = (int64_t)((p->T + 255) / 256) * k.tiles_n;
+    const char* force = getenv("MAGI_LINEAR_MT");
+    const int mt = force ? (force[0] == '1' ? 1 : 2) : (tiles256 >= 2 * ctx->sm_count ? 2 : 1);
+    k.tiles_m = (p->T + mt * 128 - 1) / (mt * 128);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    rc = mt == 2 ? launch_lp_rot<2>(ctx, rot, tx, tw, k, st) : launch_lp_rot<1>(ctx, rot, tx, tw, k, st);
+  }
+  if (prev != ctx->device) cudaSetDevice(prev);
+  return rc;
+}

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libmagi_attn.so")
 MAGI_OK = 0
 E_BADARG, E_ALIGN, E_ARCH, E_RANGE, E_NOMEM, E_NCCL, E_TIMEOUT, E_CUDA = -1, -2, -3, -4, -5, -6, -7, -8
 DTYPE_BF16, DTYPE_FP8_E4M3, DTYPE_F32 = 0, 1, 2
-NORM_LAYERNORM_1P, NORM_RMSNORM_1P = 0, 1
+NORM_LAYERNORM_1P, NORM_RMSNORM_1P, NORM_NONE = 0, 1, 2
 
 EXPORTS = [
     "magi_version", "magi_strerror", "magi_ctx_create", "magi_ctx_destroy", "magi_last_error", "magi_ctx_status",
@@ -19,7 +19,7 @@ EXPORTS = [
     "magi_kv_cache_append", "magi_kv_cache_evict", "magi_kv_cache_read", "magi_kv_cache_bytes",
     "magi_chunk_attn_fwd", "magi_chunk_attn_fwd_simt", "magi_quantize_e4m3_block128", "magi_chunk_attn_fwd_noalloc",
     "magi_peer_alloc", "magi_peer_open", "magi_peer_close", "magi_peer_free", "magi_selftest_bounded_wait",
-    "magi_bias_modulate_add", "magi_div_clamp_to_e4m3",
+    "magi_bias_modulate_add", "magi_div_clamp_to_e4m3", "magi_linear_qk_norm_rope_fwd",
     "magi_ulysses_unique_id", "magi_ulysses_create", "magi_ulysses_destroy", "magi_ulysses_a2a_in", "magi_ulysses_a2a_out",
 ]
 
@@ -34,6 +34,18 @@ class PrologueParams(C.Structure):
         ("out", C.c_void_p), ("out_stride_t", C.c_int64), ("out_stride_h", C.c_int64), ("out_stride_block", C.c_int64),
         ("heads_per_block", C.c_int32), ("out_block_ptrs", C.POINTER(C.c_void_p)),
         ("x_heads_per_block", C.c_int32), ("x_stride_block", C.c_int64),
+    ]
+
+
+class LinearPrologueParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("norm_mode", C.c_int32),
+        ("x", C.c_void_p), ("x_stride", C.c_int64), ("w", C.c_void_p), ("w_stride", C.c_int64),
+        ("T", C.c_int32), ("H", C.c_int32), ("in_features", C.c_int32), ("eps", C.c_float),
+        ("gamma", C.c_void_p), ("beta", C.c_void_p), ("rot_pairs", C.c_int32), ("heads_per_block", C.c_int32),
+        ("cos", C.c_void_p), ("sin", C.c_void_p),
+        ("out", C.c_void_p), ("out_stride_t", C.c_int64), ("out_stride_h", C.c_int64), ("out_stride_block", C.c_int64),
+        ("out_block_ptrs", C.POINTER(C.c_void_p)),
     ]
 
 
@@ -100,6 +112,7 @@ def _load():
         "magi_ulysses_a2a_out": (C.c_int, [vp, vp, vp, i64, vp]),
         "magi_qk_norm_rope_fwd": (C.c_int, [vp, C.POINTER(PrologueParams), vp]),
         "magi_head_block_copy": (C.c_int, [vp, C.POINTER(PrologueParams), vp]),
+        "magi_linear_qk_norm_rope_fwd": (C.c_int, [vp, C.POINTER(LinearPrologueParams), vp]),
         "magi_kv_cache_create": (C.c_int, [vp, C.POINTER(KVCacheDesc), C.POINTER(vp)]),
         "magi_kv_cache_destroy": (C.c_int, [vp]),
         "magi_kv_cache_append": (C.c_int, [vp, i32, i32, vp, i64, i64, vp, i64, i64, i32, i32, vp]),

@@ -13,7 +13,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import AttnParams, KVCacheDesc, ModulateParams, PrologueParams, check, lib
+from ._lib import AttnParams, KVCacheDesc, LinearPrologueParams, ModulateParams, PrologueParams, check, lib
 
 HEAD_DIM = 128
 
@@ -116,6 +116,48 @@ def qk_norm_rope(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tens
         p.rot_pairs, p.cos, p.sin = cos.shape[1], cos.data_ptr(), sin.data_ptr()
     keep = _fill_out(p, out, T, H, heads_per_block, block_out)
     check(lib.magi_qk_norm_rope_fwd(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
+    KERNEL_LAUNCHES[0] += 1
+    return out
+
+
+def linear_qk_norm_rope(x: torch.Tensor, weight: torch.Tensor, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor],
+                        cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], eps: float = 1e-6,
+                        norm_mode: str = "layernorm_1p", out: Optional[torch.Tensor] = None, heads_per_block: int = 0,
+                        stream=None, block_out=None) -> torch.Tensor:
+    """get_q / get_k / get_v from the projection on (dit_module.py:953-963, :970-980, :987-989), one kernel:
+    x bf16 [T, in_features] (the output of forward_ln), weight bf16 [H*128, in_features] (torch.nn.Linear.weight of
+    linear_qkv.q / .k / .v) -> bf16 [T, H, 128] = prologue(bf16(x @ weight^T)).  norm_mode "none" is get_v.
+    Destination (out, heads_per_block, block_out) as qk_norm_rope."""
+    for t, name in ((x, "x"), (weight, "weight")):
+        if t.dtype != torch.bfloat16 or not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+            raise ValueError(f"{name} must be a CUDA bf16 matrix with a contiguous last dim")
+    T, K = x.shape
+    if weight.shape[1] != K or weight.shape[0] % HEAD_DIM:
+        raise ValueError("weight must be [H*128, in_features]")
+    H = weight.shape[0] // HEAD_DIM
+    ctx = Context.get(x.device)
+    if out is None and block_out is None:
+        out = torch.empty(T, H, HEAD_DIM, dtype=torch.bfloat16, device=x.device)
+    p = LinearPrologueParams()
+    p.struct_size = C.sizeof(LinearPrologueParams)
+    p.norm_mode = {"layernorm_1p": _lib.NORM_LAYERNORM_1P, "rmsnorm": _lib.NORM_RMSNORM_1P, "none": _lib.NORM_NONE}[norm_mode]
+    p.x, p.x_stride, p.w, p.w_stride, p.T, p.H, p.in_features = x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), T, H, K
+    p.eps = eps
+    if norm_mode != "none":
+        gamma = gamma.to(device=x.device, dtype=torch.float32).contiguous()
+        p.gamma = gamma.data_ptr()
+        if beta is not None:
+            beta = beta.to(device=x.device, dtype=torch.float32).contiguous()
+            p.beta = beta.data_ptr()
+        if cos is not None:
+            cos = cos.to(device=x.device, dtype=torch.float32).contiguous()
+            sin = sin.to(device=x.device, dtype=torch.float32).contiguous()
+            assert cos.shape == sin.shape and cos.shape[0] == T
+            p.rot_pairs, p.cos, p.sin = cos.shape[1], cos.data_ptr(), sin.data_ptr()
+    if T == 0:
+        return out
+    keep = _fill_out(p, out, T, H, heads_per_block, block_out)
+    check(lib.magi_linear_qk_norm_rope_fwd(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
     KERNEL_LAUNCHES[0] += 1
     return out
 

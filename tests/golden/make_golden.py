@@ -32,6 +32,10 @@ What is produced (all seeded, small enough to commit):
   div_clamp.npz  the reference's div_clamp_to (dit_module.py:364-384) on bf16 activations with a per-channel and a
                  scalar scale: values around and beyond the e4m3 range, subnormal results, exact ties of both roundings.
 
+  linear_prologue.npz  get_q / get_k / get_v from their first line: the reference's CustomLayerNormLinear
+                 (dit_module.py:390-425, bf16 torch.nn.Linear members) forward_q / forward_k / forward_v on CPU, then
+                 the reference's FusedLayerNorm and flash-attn's pure-torch rotary, in get_q's order (:953-963).
+
 The reference holds no attention fixture of its own; see the oracle's header.
 """
 import argparse
@@ -356,6 +360,41 @@ def gen_div_clamp(ref_mod, out_dir):
     np.savez_compressed(os.path.join(out_dir, "div_clamp.npz"), **out)
 
 
+def gen_linear_prologue(ref_mod, out_dir):
+    from flash_attn.layers.rotary import apply_rotary_emb_torch
+    g = torch.Generator().manual_seed(23)
+    T, K, Hq, Hkv, D = 136, 128, 3, 1, 128
+    mcfg = types.SimpleNamespace(apply_layernorm_1p=True, layernorm_epsilon=1e-6, params_dtype=torch.bfloat16, num_layers=4)
+    ecfg = types.SimpleNamespace(fp8_quant=False)
+    lin = ref_mod.CustomLayerNormLinear(K, Hq * D, Hkv * D, 1, mcfg, ecfg)
+    with torch.no_grad():
+        for name in ("q", "k", "v"):
+            getattr(lin, name).weight.copy_((torch.randn(getattr(lin, name).weight.shape, generator=g) * K ** -0.5).to(torch.bfloat16))
+    x = (torch.randn(T, 1, K, generator=g) * 1.3).to(torch.bfloat16)          # [sq, b, hidden]: the output of forward_ln
+    ncfg = types.SimpleNamespace(apply_layernorm_1p=True, layernorm_epsilon=1e-6, params_dtype=torch.float32)
+    out = {"x": bf16_bits(x[:, 0])}
+    sin, cos = ref_mod.build_rotary_pos_embed(
+        [2, 4, 17], bands=ref_mod.freq_bands(16, step=1), dim=128, in_pixels=False,
+        ref_feat_shape=[2, 4 / math.sqrt(68 / 256), 17 / math.sqrt(68 / 256)])
+    out["sin"], out["cos"] = sin.numpy(), cos.numpy()
+    with torch.no_grad():
+        for name, fwd in (("q", lin.forward_q), ("k", lin.forward_k)):
+            gamma = 0.1 * torch.randn(D, generator=g)
+            beta = 0.02 * torch.randn(D, generator=g)
+            ln = ref_mod.FusedLayerNorm(ncfg, D)
+            ln.weight.copy_(gamma)
+            ln.bias.copy_(beta)
+            y = fwd(x)                                                          # bf16 [sq, b, hn * hd]
+            y = y.reshape(y.size(0), y.size(1), -1, D).float()
+            y = ln(y).transpose(0, 1).contiguous()                              # b sq hn hd
+            r = apply_rotary_emb_torch(y, cos, sin).to(torch.bfloat16)[0]       # (sq b) hn hd with b = 1
+            out["w" + name], out["gamma_" + name], out["beta_" + name] = bf16_bits(getattr(lin, name).weight), gamma.numpy(), beta.numpy()
+            out[name] = bf16_bits(r)
+        out["wv"] = bf16_bits(lin.v.weight)
+        out["v"] = bf16_bits(lin.forward_v(x)[:, 0].reshape(T, Hkv, D))
+    np.savez_compressed(os.path.join(out_dir, "linear_prologue.npz"), **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", required=True, help="root of the MAGI-1 checkout")
@@ -364,7 +403,7 @@ def main():
     a = ap.parse_args()
     sys.path.insert(0, a.ref)
     only = set(a.only.split(",")) if a.only else None
-    if only is None or "prologue" in only or "rope" in only or "modulate" in only or "div_clamp" in only:
+    if only is None or only & {"prologue", "rope", "modulate", "div_clamp", "linear_prologue"}:
         import inference.model.dit.dit_module as ref_mod
         if only is None or "prologue" in only:
             gen_prologue(ref_mod, a.out)
@@ -374,6 +413,8 @@ def main():
             gen_modulate(ref_mod, a.out)
         if only is None or "div_clamp" in only:
             gen_div_clamp(ref_mod, a.out)
+        if only is None or "linear_prologue" in only:
+            gen_linear_prologue(ref_mod, a.out)
     if only is None or "attn" in only:
         gen_attn_cfg0(a.out)
     if only is None or "ulysses" in only:

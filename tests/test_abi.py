@@ -52,6 +52,9 @@ def test_struct_layouts_match_the_header(tmp_path):
         "magi_kv_cache_desc": ["dtype", "chunk_tokens", "n_kv_heads"],
         "magi_modulate_params": ["x", "residual", "residual_dtype", "gate", "gate_stride", "condition_map", "n_gates", "gamma",
                                  "eps", "gamma_plus_one", "out", "out_stride", "rows", "hidden"],
+        "magi_linear_prologue_params": ["x", "x_stride", "w", "w_stride", "T", "H", "in_features", "eps", "gamma", "beta",
+                                        "rot_pairs", "heads_per_block", "cos", "sin", "out", "out_stride_t", "out_stride_h",
+                                        "out_stride_block", "out_block_ptrs"],
     }
     body = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]
     for s, fs in fields.items():
@@ -64,7 +67,7 @@ def test_struct_layouts_match_the_header(tmp_path):
     subprocess.check_call(["gcc", str(probe), "-o", str(exe)])
     out = subprocess.check_output([str(exe)], text=True).split("\n")
     mirror = {"magi_attn_params": L.AttnParams, "magi_prologue_params": L.PrologueParams, "magi_kv_cache_desc": L.KVCacheDesc,
-              "magi_modulate_params": L.ModulateParams}
+              "magi_modulate_params": L.ModulateParams, "magi_linear_prologue_params": L.LinearPrologueParams}
     for line in out:
         if not line:
             continue

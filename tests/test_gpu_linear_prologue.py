@@ -1,0 +1,115 @@
+"""Parity of the projection GEMM with the prologue in its epilogue (get_q / get_k / get_v from their first line,
+dit_module.py:953-989) against the reference-generated fixture, the CPU oracle and the unfused CUDA path."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import chunk_attn_oracle as O
+from gpu_util import assert_close
+
+pytestmark = pytest.mark.gpu
+
+# The accumulation order of a GEMM is not the reference's: an accumulator that lands next to a bf16 rounding boundary may
+# round the other way (one bf16 ulp of the pre-norm value, 2^-8 relative), which the norm passes on scaled by
+# (gamma + 1) / std.  Everything else follows the reference's order of operations.
+MAX_ABS = 4e-2
+MIN_COS = 0.99999
+
+
+@pytest.fixture(scope="module")
+def mb():
+    import magi_b200
+    return magi_b200
+
+
+def _bf16(bits):
+    return torch.from_numpy(bits.copy()).view(torch.bfloat16)
+
+
+def test_linear_prologue_matches_reference_fixture(mb, golden_dir):
+    """136 tokens (one ragged row tile), 3 Q heads (an odd head count: half of the last channel block is empty), 1 KV head."""
+    z = np.load(os.path.join(golden_dir, "linear_prologue.npz"))
+    x = _bf16(z["x"]).cuda()
+    cos, sin = torch.from_numpy(z["cos"]), torch.from_numpy(z["sin"])
+    for name in ("q", "k"):
+        out = mb.linear_qk_norm_rope(x, _bf16(z["w" + name]).cuda(), torch.from_numpy(z["gamma_" + name]),
+                                     torch.from_numpy(z["beta_" + name]), cos, sin)
+        torch.cuda.synchronize()
+        assert mb.Context.get().status() == 0
+        ref = _bf16(z[name])
+        assert_close(out, ref, max_abs=MAX_ABS, min_cos=MIN_COS, what=name)
+        assert (out.cpu().view(torch.int16) != ref.view(torch.int16)).float().mean().item() < 0.05
+    v = mb.linear_qk_norm_rope(x, _bf16(z["wv"]).cuda(), None, None, None, None, norm_mode="none")
+    torch.cuda.synchronize()
+    ref = _bf16(z["v"])
+    assert (v.cpu().view(torch.int16) != ref.view(torch.int16)).float().mean().item() < 0.01
+    assert_close(v, ref, max_abs=2 ** -5, min_cos=MIN_COS, what="v")
+
+
+@pytest.mark.parametrize("mode", ["layernorm_1p", "rmsnorm", "none"])
+def test_both_tile_shapes_against_oracle_and_unfused_path(mb, mode, monkeypatch):
+    """19000 tokens x 1024 features x 8 heads: 16 k-blocks per tile (the ring wraps), several tiles per CTA, a ragged last
+    row tile; the 128-row and the 256-row form accumulate in the same order and must agree bit for bit."""
+    g = torch.Generator().manual_seed(31)
+    T, K, H = 19000, 1024, 8
+    x = (torch.randn(T, K, generator=g) * 1.2).to(torch.bfloat16)
+    w = (torch.randn(H * 128, K, generator=g) * K ** -0.5).to(torch.bfloat16)
+    gam, bet, _, _ = O.make_norm_params(5)
+    sin, cos = O.rope_table(8, 25, 95)
+    assert sin.shape[0] == T
+    xd, wd = x.cuda(), w.cuda()
+    outs = []
+    for mt in ("1", "2"):
+        monkeypatch.setenv("MAGI_LINEAR_MT", mt)
+        outs.append(mb.linear_qk_norm_rope(xd, wd, gam, bet, cos, sin, norm_mode=mode))
+        torch.cuda.synchronize()
+        assert mb.Context.get().status() == 0
+    monkeypatch.delenv("MAGI_LINEAR_MT")
+    assert torch.equal(outs[0], outs[1])
+    rows = torch.cat([torch.arange(0, 300), torch.arange(9400, 9700), torch.arange(T - 300, T), torch.randint(0, T, (400,), generator=g)])
+    ref = O.linear_qk_prologue(x[rows], w, gam, bet, cos[rows], sin[rows], norm_mode=mode)
+    assert_close(outs[0][rows.cuda()], ref, max_abs=MAX_ABS, min_cos=MIN_COS, what=f"fused {mode}")
+    # the unfused CUDA path: library GEMM, then the prologue kernel
+    y = (xd @ wd.t()).view(T, H, 128)
+    unfused = y if mode == "none" else mb.qk_norm_rope(y, gam, bet, cos, sin, norm_mode=mode)
+    torch.cuda.synchronize()
+    assert_close(outs[0], unfused, max_abs=MAX_ABS, min_cos=MIN_COS, what=f"fused vs unfused {mode}")
+
+
+def test_destination_layouts_and_strided_operands(mb):
+    """x and W as column slices of wider tensors (the fused QKV weight), the result written as the Ulysses send layout
+    "(cp seq) hn hd" (context_parallel.py:396) and into a K|V fused buffer (dit_module.py:991-996)."""
+    g = torch.Generator().manual_seed(32)
+    T, K, H, cp = 700, 384, 4, 2
+    xw = (torch.randn(T, K + 128, generator=g)).to(torch.bfloat16).cuda()
+    ww = (torch.randn(3 * H * 128, K + 256, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    x, w = xw[:, 128:], ww[H * 128:2 * H * 128, 256:]
+    gam, bet, _, _ = O.make_norm_params(6)
+    sin, cos = O.rope_table(2, 10, 35)
+    packed = mb.linear_qk_norm_rope(x, w, gam, bet, cos, sin)
+    ref = O.linear_qk_prologue(x.cpu(), w.cpu(), gam, bet, cos, sin)
+    assert_close(packed, ref, max_abs=MAX_ABS, min_cos=MIN_COS, what="strided operands")
+    send = torch.zeros(cp, T, H // cp, 128, dtype=torch.bfloat16, device="cuda")
+    mb.linear_qk_norm_rope(x, w, gam, bet, cos, sin, out=send, heads_per_block=H // cp)
+    assert torch.equal(send.permute(1, 0, 2, 3).reshape(T, H, 128), packed)
+    kv = torch.zeros(T, H, 256, dtype=torch.bfloat16, device="cuda")
+    mb.linear_qk_norm_rope(x, w, gam, bet, cos, sin, out=kv[:, :, :128])
+    mb.linear_qk_norm_rope(x, w, None, None, None, None, norm_mode="none", out=kv[:, :, 128:])
+    torch.cuda.synchronize()
+    assert torch.equal(kv[:, :, :128], packed)
+    assert_close(kv[:, :, 128:], O.linear_qk_prologue(x.cpu(), w.cpu(), None, None, None, None, norm_mode="none"),
+                 max_abs=2 ** -5, min_cos=MIN_COS, what="v into the fused buffer")
+
+
+def test_bad_arguments_are_refused_on_the_host(mb):
+    x = torch.zeros(64, 192, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(128, 192, dtype=torch.bfloat16, device="cuda")
+    gam, bet, _, _ = O.make_norm_params(1)
+    with pytest.raises(mb.MagiError, match="multiple of 128"):
+        mb.linear_qk_norm_rope(x, w, gam, bet, None, None)
+    x, w = torch.zeros(64, 256, dtype=torch.bfloat16, device="cuda"), torch.zeros(128, 256, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(mb.MagiError, match="rot_pairs"):
+        mb.linear_qk_norm_rope(x, w, gam, bet, torch.zeros(64, 40), torch.zeros(64, 40))
+    assert mb.linear_qk_norm_rope(x[:0], w, gam, bet, None, None).shape == (0, 1, 128)

@@ -29,6 +29,25 @@ def test_prologue_matches_reference_layernorm_and_rotary(golden_dir):
     assert (got.view(torch.int16) != ref.view(torch.int16)).float().mean() < 1e-3
 
 
+def test_linear_prologue_matches_reference_projection_and_get_q(golden_dir):
+    """The reference's bf16 torch.nn.Linear (fp32 accumulation, one rounding) against the oracle's exactly rounded matmul:
+    an accumulator next to a bf16 rounding boundary may differ by one ulp before the norm, nothing else may."""
+    z = np.load(os.path.join(golden_dir, "linear_prologue.npz"))
+    x = _bf16(z["x"])
+    sin, cos = torch.from_numpy(z["sin"]), torch.from_numpy(z["cos"])
+    for name in ("q", "k"):
+        got = O.linear_qk_prologue(x, _bf16(z["w" + name]), torch.from_numpy(z["gamma_" + name]), torch.from_numpy(z["beta_" + name]), cos, sin)
+        ref = _bf16(z[name])
+        assert got.shape == ref.shape
+        assert (got.float() - ref.float()).abs().max() <= 4e-2
+        assert (got.view(torch.int16) != ref.view(torch.int16)).float().mean() < 0.02
+        assert O.cosine(got, ref) > 0.999999
+    v = O.linear_qk_prologue(x, _bf16(z["wv"]), None, None, None, None, norm_mode="none")
+    ref = _bf16(z["v"])
+    assert (v.view(torch.int16) != ref.view(torch.int16)).float().mean() < 5e-3
+    assert (v.float() - ref.float()).abs().max() <= 2 ** -6
+
+
 def test_rope_table_matches_reference_builder(golden_dir):
     z = np.load(os.path.join(golden_dir, "rope.npz"))
     for name in ("a", "b", "c"):
