@@ -10,16 +10,20 @@
 // is rounded to bf16 before the norm, as the reference's Linear rounds its output.
 //
 // GEMM: x [T, K] and W [H*128, K] are both K-major, so both operands come in by TMA (128-byte swizzle, 64 k-elements per
-// stage) and go to tcgen05.mma straight from shared memory.  CTA tile = (kMT x 128) tokens x 256 channels (two heads):
-// kMT = 2 uses all 512 TMEM columns for one tile and loads 64 KB per 8 UMMAs (64 B per cycle per SM from L2); kMT = 1
-// keeps two 256-column accumulators so that the epilogue of a tile overlaps the main loop of the next, at 96 B per cycle.
+// stage) and go to tcgen05.mma straight from shared memory; two 256-column accumulators in TMEM, so the epilogue of a
+// tile overlaps the main loop of the next.  Two forms:
+//   pair  a cluster of two CTAs works on 256 tokens x 256 channels with tcgen05.mma.cta_group::2 (M = 256): each CTA
+//         loads its own 128 tokens of x and only ITS HALF of the W tile (32 KB per stage instead of 48, six stages),
+//         the tensor cores of the two SMs share the W halves, and each CTA drains its own 128 rows.  Every load goes
+//         to the loading CTA's own shared memory only; the odd CTA's loads count their bytes on the even CTA's barrier,
+//         and the issuer commits "stage free" and "accumulator ready" to each CTA's barrier in turn.
+//   solo  one CTA, 128 tokens x 256 channels, tcgen05.mma.cta_group::1, four 48 KB stages: small problems.
 //
-//   warp 0      TMA producer (one thread): A and B k-blocks into a ring of stages
-//   warp 1      UMMA issuer (one thread)
-//   warps 2-9   epilogue: warp w drains TMEM lane quarter w % 4; kMT = 2: warps 2-5 take one row tile, 6-9 the other, both
-//               heads each; kMT = 1: warps 2-5 take head 0 of the tile, 6-9 head 1
-// Persistent: CTA b takes tiles b, b + grid, ...; tiles are numbered with the channel block fastest, so the CTAs running
-// at any time share a few row blocks of x and all of W through L2.  Every wait is bounded (MAGI_E_TIMEOUT).
+//   warp 0      TMA producer (one thread): x and W k-blocks into a ring of stages
+//   warp 1      UMMA issuer (one thread; in a pair the even CTA's)
+//   warps 2-9   epilogue: warp w drains TMEM lane quarter w % 4; warps 2-5 take the tile's first head, 6-9 its second
+// Persistent: cluster (or CTA) b takes tiles b, b + grid, ...; tiles are numbered with the channel block fastest, so the
+// CTAs running at any time share a few row blocks of x and all of W through L2.  Every wait is bounded (MAGI_E_TIMEOUT).
 #include <cuda_bf16.h>
 #include <math.h>
 #include <stdlib.h>
@@ -38,21 +42,20 @@ constexpr int kLpKBlock = 64;                                  // k-elements per
 constexpr int kLpSlab = 128 * kLpKBlock * 2;                   // 128 rows x 128 bytes = 16 KB
 constexpr int kLpTileN = 256;                                  // two heads
 
-template <int kMT>
+template <bool kPair>
 struct SmemLp {
-  static constexpr int kStageBytes = (kMT + 2) * kLpSlab;      // A: kMT slabs, B: two slabs (256 channels)
-  static constexpr int kStages = kMT == 2 ? 3 : 4;             // 192 KB either way
-  static constexpr int kAccSets = 2 / kMT;                     // TMEM: kAccSets x kMT x 256 columns = 512
+  static constexpr int kStageBytes = (kPair ? 2 : 3) * kLpSlab;  // x: one slab; W: one slab (this CTA's half) or two
+  static constexpr int kStages = kPair ? 6 : 4;                  // 192 KB either way
   static constexpr int kRing = 0;
-  static constexpr int kStore = kStages * kStageBytes;         // 8 epilogue warps x 4 KB: 32 rows x 64 channels bf16
+  static constexpr int kStore = kStages * kStageBytes;           // 8 epilogue warps x 4 KB: 32 rows x 64 channels bf16
   static constexpr int kBar = kStore + 8 * 4096;
-  static constexpr int kNumBars = 2 * kStages + 2 * kAccSets;  // full, empty, acc_full, acc_empty
-  static constexpr int kMisc = kBar + kNumBars * 8;            // tmem slot, abort flag
-  static constexpr int kGamma = kMisc + 16;                    // float (gamma + 1)[128], beta[128]
+  static constexpr int kNumBars = 2 * kStages + 4;               // full, empty, acc_full[2], acc_empty[2]
+  static constexpr int kMisc = kBar + kNumBars * 8;              // tmem slot, abort flag
+  static constexpr int kGamma = kMisc + 16;                      // float (gamma + 1)[128], beta[128]
   static constexpr int kTotal = kGamma + 1024;
-  static constexpr int kDynamic = kTotal + 1024;               // slack to align the base to 1024 bytes
+  static constexpr int kDynamic = kTotal + 1024;                 // slack to align the base to 1024 bytes
 };
-static_assert(SmemLp<1>::kDynamic <= 232448 && SmemLp<2>::kDynamic <= 232448, "shared memory per CTA");
+static_assert(SmemLp<false>::kDynamic <= 232448 && SmemLp<true>::kDynamic <= 232448, "shared memory per CTA");
 
 struct LinearPrologueKernelParams {
   int T, H, k_blocks;
@@ -127,32 +130,68 @@ __device__ __forceinline__ void head_epilogue(float (&v)[kHeadDim], uint32_t (&o
   for (int c = 0; c < kHeadDim / 2; ++c) o[c] = pack_bf16x2(v[2 * c], v[2 * c + 1]);
 }
 
-template <int kMT, int kRot>
+
+// One head (128 accumulator values per thread) of this warp's 32 rows: norm + rotary in registers, then the
+// store, staged through 4 KB of shared memory per warp, 64 channels at a time, so that the global stores are whole
+// 128-byte pieces of a row (eight lanes per row, four rows per instruction); 16-byte chunks XOR-swizzled by the row.
+template <int kRot>
+__device__ __forceinline__ void store_head(float (&v)[kHeadDim], const LinearPrologueKernelParams& p, const float* g_sh,
+                                           const float* b_sh, uint8_t* stage_sh, int head, int row0, int lane) {
+  uint32_t o[kHeadDim / 2];
+  head_epilogue<kRot>(v, o, p, g_sh, b_sh, (int64_t)row0 + lane, row0 + lane < p.T);
+  // destination of (token, head): block of heads, then the row inside it
+  const int blk = p.heads_per_block > 0 ? head / p.heads_per_block : 0;
+  const int hs = p.heads_per_block > 0 ? head - blk * p.heads_per_block : head;
+  __nv_bfloat16* base = (p.use_block_ptrs ? p.out_blocks[blk] : p.out + blk * p.out_stride_block) + hs * p.out_stride_h;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    __syncwarp();
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      *reinterpret_cast<uint4*>(stage_sh + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+          make_uint4(o[half * 32 + 4 * c], o[half * 32 + 4 * c + 1], o[half * 32 + 4 * c + 2], o[half * 32 + 4 * c + 3]);
+    __syncwarp();
+    const int l8 = lane & 7, rsel = lane >> 3;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = 4 * i + rsel;
+      if (row0 + rr < p.T) {
+        const uint4 val = *reinterpret_cast<const uint4*>(stage_sh + rr * 128 + ((l8 ^ (rr & 7)) << 4));
+        *reinterpret_cast<uint4*>(base + (int64_t)(row0 + rr) * p.out_stride_t + half * 64 + l8 * 8) = val;
+      }
+    }
+  }
+}
+
+template <bool kPair, int kRot>
 __global__ void __launch_bounds__(kLpThreads, 1)
 linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                        const LinearPrologueKernelParams p) {
-  using L = SmemLp<kMT>;
+  using L = SmemLp<kPair>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
-  uint64_t* full = bars;
-  uint64_t* empty = full + L::kStages;
+  uint64_t* full = bars;                      // the stage is loaded (TMA transaction bytes; pair: both CTAs' stage, even CTA's barrier)
+  uint64_t* empty = full + L::kStages;        // the UMMAs that read the stage have completed
   uint64_t* acc_full = empty + L::kStages;
-  uint64_t* acc_empty = acc_full + L::kAccSets;
+  uint64_t* acc_empty = acc_full + 2;         // pair: the even CTA's barrier collects both CTAs' epilogue warps
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
   float* g_sh = reinterpret_cast<float*>(smem + L::kGamma);
   float* b_sh = g_sh + kHeadDim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = kPair ? cluster_ctarank() : 0;  // 0: issues the UMMAs
+  const int unit = kPair ? blockIdx.x >> 1 : blockIdx.x, n_units = kPair ? gridDim.x >> 1 : gridDim.x;
+  constexpr int kTileRows = kPair ? 256 : 128;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::kStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int a = 0; a < L::kAccSets; ++a) {
+    for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 8);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[a], kPair ? 16 : 8);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -162,11 +201,18 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     b_sh[threadIdx.x] = (p.norm_mode == MAGI_NORM_LAYERNORM_1P && p.beta) ? p.beta[threadIdx.x] : 0.0f;
   }
   if (warp == 0) {
+    // all 512 columns, by each CTA for itself: in a pair both CTAs then hold the same columns at the same address,
+    // which is what a pair UMMA writes to (checked below)
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (kPair) {
+    cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+    if (threadIdx.x == 0 && ld_cluster_u32(mapa_u32(tmem_slot, rank ^ 1)) != *tmem_slot) *abort_flag = 1;
+    __syncthreads();
+  }
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const int n_tiles = p.tiles_m * p.tiles_n;
@@ -174,62 +220,88 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (lane == 0 && !*abort_flag) {
       tma_prefetch_desc(&tm_x);
       tma_prefetch_desc(&tm_w);
       int fill = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int row0 = (tile / p.tiles_n) * (kMT * 128), ch0 = (tile % p.tiles_n) * kLpTileN;
+      const uint32_t full_0 = kPair ? mapa_u32(&full[0], 0) : 0;
+      for (int tile = unit; tile < n_tiles && ok; tile += n_units) {
+        const int row0 = (tile / p.tiles_n) * kTileRows + rank * 128;
+        const int ch0 = (tile % p.tiles_n) * kLpTileN + (kPair ? rank * 128 : 0);
         for (int kb = 0; kb < p.k_blocks; ++kb, ++fill) {
           const int stage = fill % L::kStages, use = fill / L::kStages;
-          if (use > 0) ok = mbar_wait(&empty[stage], (use & 1) ^ 1, abort_flag);
+          // the stage is free once the UMMAs that read it have completed (in a pair the issuer commits to both CTAs)
+          if (use > 0) ok = kPair ? mbar_wait_cluster(&empty[stage], (use & 1) ^ 1, abort_flag) : mbar_wait(&empty[stage], (use & 1) ^ 1, abort_flag);
           if (!ok) break;
           uint8_t* dst = ring + stage * L::kStageBytes;
-          mbar_expect_tx(&full[stage], L::kStageBytes);
           // x and W are seen as [rows, K / 128, 128]: k-block kb is the half (kb & 1) of 128-column group kb >> 1
           const int c0 = (kb & 1) * kLpKBlock, c1 = kb >> 1;
-#pragma unroll
-          for (int m = 0; m < kMT; ++m) tma_load_3d(dst + m * kLpSlab, &tm_x, &full[stage], c0, c1, row0 + m * 128);
-          tma_load_3d(dst + kMT * kLpSlab, &tm_w, &full[stage], c0, c1, ch0);
-          tma_load_3d(dst + (kMT + 1) * kLpSlab, &tm_w, &full[stage], c0, c1, ch0 + 128);
+          if constexpr (kPair) {
+            // both CTAs' loads of a stage count on the EVEN CTA's barrier, which its producer arms for both
+            if (rank == 0) mbar_expect_tx(&full[stage], 2 * L::kStageBytes);
+            const uint32_t bar = rank == 0 ? smem_u32(&full[stage]) : full_0 + stage * 8;
+            tma_load_3d_pair(dst, &tm_x, bar, c0, c1, row0);
+            tma_load_3d_pair(dst + kLpSlab, &tm_w, bar, c0, c1, ch0);
+          } else {
+            mbar_expect_tx(&full[stage], L::kStageBytes);
+            tma_load_3d(dst, &tm_x, &full[stage], c0, c1, row0);
+            tma_load_3d(dst + kLpSlab, &tm_w, &full[stage], c0, c1, ch0);
+            tma_load_3d(dst + 2 * kLpSlab, &tm_w, &full[stage], c0, c1, ch0 + 128);
+          }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(128, kLpTileN, 1, 1, 0, 0);
-      constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO = 1024 B, version 1, 128-byte swizzle
-      const uint32_t ring_lo = (smem_u32(ring) >> 4) | (1u << 16);         // K-major: LBO field = 1
-      int fill = 0, t_local = 0;
+    if (lane == 0 && !*abort_flag) {
+      int fill = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t_local) {
-        const int a = t_local % L::kAccSets, a_use = t_local / L::kAccSets;
-        if (a_use > 0) ok = mbar_wait(&acc_empty[a], (a_use & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t tD = tmem_base + a * (kMT * kLpTileN);
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++fill) {
-          const int stage = fill % L::kStages;
-          ok = mbar_wait(&full[stage], (uint32_t)(fill / L::kStages) & 1, abort_flag);
+      if (!(kPair && rank == 1)) {
+        // ---------------------------------------------------------------- UMMA issuer
+        constexpr uint32_t idesc = umma_idesc(kTileRows, kLpTileN, 1, 1, 0, 0);
+        constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO = 1024 B, version 1, 128-byte swizzle
+        const uint32_t ring_lo = (smem_u32(ring) >> 4) | (1u << 16);         // K-major: LBO field = 1
+        const uint32_t empty_1 = kPair ? mapa_u32(&empty[0], 1) : 0, acc_full_1 = kPair ? mapa_u32(&acc_full[0], 1) : 0;
+        int t_local = 0;
+        for (int tile = unit; tile < n_tiles && ok; tile += n_units, ++t_local) {
+          const int a = t_local & 1, a_use = t_local >> 1;
+          if (a_use > 0) ok = kPair ? mbar_wait_cluster(&acc_empty[a], (a_use & 1) ^ 1, abort_flag) : mbar_wait(&acc_empty[a], (a_use & 1) ^ 1, abort_flag);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t s_lo = ring_lo + stage * (L::kStageBytes >> 4);
-          const uint32_t b_lo = s_lo + kMT * (kLpSlab >> 4);
+          const uint32_t d = tmem_base + a * kLpTileN;
+          for (int kb = 0; kb < p.k_blocks; ++kb, ++fill) {
+            const int stage = fill % L::kStages;
+            const uint32_t par = (uint32_t)(fill / L::kStages) & 1;
+            ok = kPair ? mbar_wait_cluster(&full[stage], par, abort_flag) : mbar_wait(&full[stage], par, abort_flag);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t a_lo = ring_lo + stage * (L::kStageBytes >> 4);
+            const uint32_t b_lo = a_lo + (kLpSlab >> 4);
+            if constexpr (kPair) {
+              if (kb == 0) umma_ss_f16_lh_pair<0>(d, a_lo, b_lo, desc_hi, idesc);
+              else umma_ss_f16_lh_pair<1>(d, a_lo, b_lo, desc_hi, idesc);
 #pragma unroll
-          for (int m = 0; m < kMT; ++m) {
-            const uint32_t a_lo = s_lo + m * (kLpSlab >> 4);
-            const uint32_t d = tD + m * kLpTileN;
-            if (kb == 0) umma_ss_f16_lh<0>(d, a_lo, b_lo, desc_hi, idesc);
-            else umma_ss_f16_lh<1>(d, a_lo, b_lo, desc_hi, idesc);
+              for (int k = 1; k < 4; ++k) umma_ss_f16_lh_pair<1>(d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);  // 16 k-elements = 32 bytes
+              umma_commit_pair(&empty[stage]);
+              umma_commit_pair_at(empty_1 + stage * 8);
+            } else {
+              if (kb == 0) umma_ss_f16_lh<0>(d, a_lo, b_lo, desc_hi, idesc);
+              else umma_ss_f16_lh<1>(d, a_lo, b_lo, desc_hi, idesc);
 #pragma unroll
-            for (int k = 1; k < 4; ++k) umma_ss_f16_lh<1>(d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);  // 16 k-elements = 32 bytes
+              for (int k = 1; k < 4; ++k) umma_ss_f16_lh<1>(d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+              umma_commit(&empty[stage]);
+            }
           }
-          umma_commit(&empty[stage]);
+          if (ok) {
+            if constexpr (kPair) {
+              umma_commit_pair(&acc_full[a]);
+              umma_commit_pair_at(acc_full_1 + a * 8);
+            } else {
+              umma_commit(&acc_full[a]);
+            }
+          }
         }
-        if (ok) umma_commit(&acc_full[a]);
       }
     }
     __syncwarp();
@@ -237,67 +309,39 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int ew = warp - 2;                 // 0..7
     const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
-    const int sel = ew >> 2;                 // kMT = 2: row tile; kMT = 1: head of the tile
+    const int hh = ew >> 2;                  // head of the tile this warp drains
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     uint8_t* stage_sh = smem + L::kStore + ew * 4096;
-    bool ok = true;
+    const uint32_t acc_empty_0 = kPair ? mapa_u32(&acc_empty[0], 0) : 0;  // the issuer's barriers
+    bool ok = !*abort_flag;
     int t_local = 0;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t_local) {
-      const int a = t_local % L::kAccSets;
-      const int row0 = (tile / p.tiles_n) * (kMT * 128) + (kMT == 2 ? sel * 128 : 0) + quarter * 32;
-      const int head0 = (tile % p.tiles_n) * 2;
-      ok = mbar_wait(&acc_full[a], (uint32_t)(t_local / L::kAccSets) & 1, abort_flag);
+    for (int tile = unit; tile < n_tiles && ok; tile += n_units, ++t_local) {
+      const int a = t_local & 1;
+      const int row0 = (tile / p.tiles_n) * kTileRows + rank * 128 + quarter * 32;
+      const int head = (tile % p.tiles_n) * 2 + hh;
+      ok = kPair ? mbar_wait_cluster(&acc_full[a], (uint32_t)(t_local >> 1) & 1, abort_flag) : mbar_wait(&acc_full[a], (uint32_t)(t_local >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t tD = tmem_base + lane_base + a * (kMT * kLpTileN) + (kMT == 2 ? sel * kLpTileN : 0);
-      const int64_t token = row0 + lane;
-      const bool row_valid = token < p.T;
-#pragma unroll 1
-      for (int hh = (kMT == 2 ? 0 : sel); hh < (kMT == 2 ? 2 : sel + 1); ++hh) {
-        const int head = head0 + hh;
-        float v[kHeadDim];
-        uint32_t o[kHeadDim / 2];
+      float v[kHeadDim];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(tD + hh * kHeadDim + c * 32, reinterpret_cast<uint32_t*>(v) + c * 32);
-        tmem_wait_ld();
-        if (hh == (kMT == 2 ? 1 : sel)) {  // the last read of this accumulator by this warp
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[a]);
-        }
-        if (head >= p.H) continue;  // warp-uniform: an odd head count leaves half of the last channel block empty
-        head_epilogue<kRot>(v, o, p, g_sh, b_sh, token, row_valid);
-        // destination of (token, head): block of heads, then the row inside it
-        const int blk = p.heads_per_block > 0 ? head / p.heads_per_block : 0;
-        const int hs = p.heads_per_block > 0 ? head - blk * p.heads_per_block : head;
-        __nv_bfloat16* base = (p.use_block_ptrs ? p.out_blocks[blk] : p.out + blk * p.out_stride_block) + hs * p.out_stride_h;
-        // staged through 4 KB of shared memory per warp, 64 channels at a time, so that the global stores are whole
-        // 128-byte pieces of a row (eight lanes per row, four rows per instruction); 16-byte chunks XOR-swizzled by row
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          __syncwarp();
-#pragma unroll
-          for (int c = 0; c < 8; ++c)
-            *reinterpret_cast<uint4*>(stage_sh + lane * 128 + ((c ^ (lane & 7)) << 4)) =
-                make_uint4(o[half * 32 + 4 * c], o[half * 32 + 4 * c + 1], o[half * 32 + 4 * c + 2], o[half * 32 + 4 * c + 3]);
-          __syncwarp();
-          const int l8 = lane & 7, rsel = lane >> 3;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int rr = 4 * i + rsel;
-            if (row0 + rr < p.T) {
-              const uint4 val = *reinterpret_cast<const uint4*>(stage_sh + rr * 128 + ((l8 ^ (rr & 7)) << 4));
-              *reinterpret_cast<uint4*>(base + (int64_t)(row0 + rr) * p.out_stride_t + half * 64 + l8 * 8) = val;
-            }
-          }
-        }
+      for (int c = 0; c < 4; ++c)
+        tmem_ld32(tmem_base + lane_base + a * kLpTileN + hh * kHeadDim + c * 32, reinterpret_cast<uint32_t*>(v) + c * 32);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {  // this warp is through with the accumulator
+        if constexpr (kPair) mbar_arrive_cluster(acc_empty_0 + a * 8);
+        else mbar_arrive(&acc_empty[a]);
       }
+      if (head < p.H)  // warp-uniform: an odd head count leaves half of the last channel block empty
+        store_head<kRot>(v, p, g_sh, b_sh, stage_sh, head, row0, lane);
     }
   }
 
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (kPair) cluster_sync_all();  // neither CTA frees its columns or leaves while the other may still signal it
   if (*abort_flag && threadIdx.x == 0 && p.status) *p.status = MAGI_E_TIMEOUT;
   if (warp == 0) {
     tc_fence_after_sync();
@@ -306,29 +350,41 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
 }
 
 // ---------------------------------------------------------------------------------------------- host side
-template <int kMT, int kRot>
+template <bool kPair, int kRot>
 static int launch_lp(magi_ctx* ctx, const CUtensorMap& tx, const CUtensorMap& tw, const LinearPrologueKernelParams& k, cudaStream_t st) {
   static bool configured[64] = {};  // per device: opt in to > 48 KB of dynamic shared memory once
   if (ctx->device < 64 && !configured[ctx->device]) {
-    MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(linear_prologue_kernel<kMT, kRot>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           SmemLp<kMT>::kDynamic));
+    MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(linear_prologue_kernel<kPair, kRot>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SmemLp<kPair>::kDynamic));
     configured[ctx->device] = true;
   }
   const int n_tiles = k.tiles_m * k.tiles_n;
-  const int grid = n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count;
-  linear_prologue_kernel<kMT, kRot><<<grid, kLpThreads, SmemLp<kMT>::kDynamic, st>>>(tx, tw, k);
-  MAGI_CUDA_OK(ctx, cudaGetLastError());
+  const int max_units = kPair ? ctx->sm_count / 2 : ctx->sm_count;
+  const int units = n_tiles < max_units ? n_tiles : max_units;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(kPair ? 2 * units : units, 1, 1);
+  cfg.blockDim = dim3(kLpThreads, 1, 1);
+  cfg.dynamicSmemBytes = SmemLp<kPair>::kDynamic;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kPair ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MAGI_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, linear_prologue_kernel<kPair, kRot>, tx, tw, k));
   return MAGI_OK;
 }
 
-template <int kMT>
+template <bool kPair>
 static int launch_lp_rot(magi_ctx* ctx, int rot, const CUtensorMap& tx, const CUtensorMap& tw, const LinearPrologueKernelParams& k,
                          cudaStream_t st) {
   switch (rot) {
-    case 0: return launch_lp<kMT, 0>(ctx, tx, tw, k, st);
-    case 32: return launch_lp<kMT, 32>(ctx, tx, tw, k, st);
-    case 48: return launch_lp<kMT, 48>(ctx, tx, tw, k, st);
-    case 64: return launch_lp<kMT, 64>(ctx, tx, tw, k, st);
+    case 0: return launch_lp<kPair, 0>(ctx, tx, tw, k, st);
+    case 32: return launch_lp<kPair, 32>(ctx, tx, tw, k, st);
+    case 48: return launch_lp<kPair, 48>(ctx, tx, tw, k, st);
+    case 64: return launch_lp<kPair, 64>(ctx, tx, tw, k, st);
   }
   return set_err(ctx, MAGI_E_BADARG, "linear prologue: rot_pairs must be 0, 32, 48 or 64 (the reference uses 48)");
 }
@@ -389,13 +445,14 @@ extern "C" int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_pro
       k.out_blocks[b] = (p->out_block_ptrs && b < p->H / p->heads_per_block) ? reinterpret_cast<__nv_bfloat16*>(p->out_block_ptrs[b]) : nullptr;
     k.tiles_n = (p->H + 1) / 2;
     k.status = reinterpret_cast<int*>(reinterpret_cast<char*>(ctx->workspace) + offsetof(PlanHeader, status));
-    // 256-row tiles (less traffic from L2 per flop) unless the problem is too small to fill the SMs with them
+    // CTA pairs unless the problem is too small to give every pair a 256-row tile; MAGI_LINEAR_FORM=solo|pair overrides
+    // (kept for A/B measurements)
     const int64_t tiles256 = (int64_t)((p->T + 255) / 256) * k.tiles_n;
-    const char* force = getenv("MAGI_LINEAR_MT");
-    const int mt = force ? (force[0] == '1' ? 1 : 2) : (tiles256 >= 2 * ctx->sm_count ? 2 : 1);
-    k.tiles_m = (p->T + mt * 128 - 1) / (mt * 128);
+    const char* force = getenv("MAGI_LINEAR_FORM");
+    const bool pair = force ? force[0] == 'p' : tiles256 >= ctx->sm_count / 2;
+    k.tiles_m = pair ? (p->T + 255) / 256 : (p->T + 127) / 128;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    rc = mt == 2 ? launch_lp_rot<2>(ctx, rot, tx, tw, k, st) : launch_lp_rot<1>(ctx, rot, tx, tw, k, st);
+    rc = pair ? launch_lp_rot<true>(ctx, rot, tx, tw, k, st) : launch_lp_rot<false>(ctx, rot, tx, tw, k, st);
   }
   if (prev != ctx->device) cudaSetDevice(prev);
   return rc;

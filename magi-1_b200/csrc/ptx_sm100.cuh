@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the attention kernels use:
-// mbarrier, TMA (cp.async.bulk.tensor, never multicast), tcgen05 (TMEM alloc, UMMA, ld/st, commit).
+// mbarrier, TMA (cp.async.bulk.tensor, never multicast), tcgen05 (TMEM alloc, UMMA, ld/st, commit), CTA pairs.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -88,6 +88,58 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, v
   return true;
 }
 
+// ---------------------------------------------------------------- CTA pairs (cluster of two)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory object in CTA `rank` of this cluster (a shared::cluster address).
+__device__ __forceinline__ uint32_t mapa_u32(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+  return r;
+}
+// One arrival on an mbarrier of another CTA of the cluster; what this thread wrote or observed before is visible to
+// whoever waits on that barrier with cluster scope.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)MAGI_WAIT_HINT_NS)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait on a barrier that a thread of the peer CTA arrives on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  long long limit_cycles = 1000000000LL) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > limit_cycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ uint32_t ld_cluster_u32(uint32_t cluster_addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+// Every thread of both CTAs arrives, then waits: the pair's start-up and tear-down barrier.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -108,6 +160,16 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+// Pair form: the destination is this CTA's shared memory, the mbarrier that receives the transaction bytes may be the
+// peer CTA's (a shared::cluster address from mapa_u32).  No multicast: the data goes to this CTA only.
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0, int c1,
+                                                 int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 
@@ -200,6 +262,29 @@ __device__ __forceinline__ void umma_ts_f16_lh(uint32_t d_tmem, uint32_t a_tmem,
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(kAccumulate)
       : "memory");
+}
+// Pair form: issued by one thread of the even CTA of a pair; M = 256 rows (128 per CTA, each CTA's A tile and half of
+// the B tile at the same shared-memory offset in both), the accumulator at the same tensor-memory address in both.
+template <int kAccumulate>
+__device__ __forceinline__ void umma_ss_f16_lh_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(kAccumulate)
+      : "memory");
+}
+// One arrival on a barrier of the issuing CTA once every pair operation issued so far by this thread has completed in
+// both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// The same with the barrier given as a shared::cluster address: it may be the peer CTA's (from mapa_u32).
+__device__ __forceinline__ void umma_commit_pair_at(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 // The mbarrier gets one arrival once every tcgen05 operation issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {

@@ -49,9 +49,10 @@ def test_linear_prologue_matches_reference_fixture(mb, golden_dir):
 
 
 @pytest.mark.parametrize("mode", ["layernorm_1p", "rmsnorm", "none"])
-def test_both_tile_shapes_against_oracle_and_unfused_path(mb, mode, monkeypatch):
+def test_both_forms_against_oracle_and_unfused_path(mb, mode, monkeypatch):
     """19000 tokens x 1024 features x 8 heads: 16 k-blocks per tile (the ring wraps), several tiles per CTA, a ragged last
-    row tile; the 128-row and the 256-row form accumulate in the same order and must agree bit for bit."""
+    row tile (the odd CTA of the last pair has 56 rows); the one-CTA form and the CTA-pair form accumulate in the same
+    order and must agree bit for bit."""
     g = torch.Generator().manual_seed(31)
     T, K, H = 19000, 1024, 8
     x = (torch.randn(T, K, generator=g) * 1.2).to(torch.bfloat16)
@@ -61,12 +62,12 @@ def test_both_tile_shapes_against_oracle_and_unfused_path(mb, mode, monkeypatch)
     assert sin.shape[0] == T
     xd, wd = x.cuda(), w.cuda()
     outs = []
-    for mt in ("1", "2"):
-        monkeypatch.setenv("MAGI_LINEAR_MT", mt)
+    for form in ("solo", "pair"):
+        monkeypatch.setenv("MAGI_LINEAR_FORM", form)
         outs.append(mb.linear_qk_norm_rope(xd, wd, gam, bet, cos, sin, norm_mode=mode))
         torch.cuda.synchronize()
         assert mb.Context.get().status() == 0
-    monkeypatch.delenv("MAGI_LINEAR_MT")
+    monkeypatch.delenv("MAGI_LINEAR_FORM")
     assert torch.equal(outs[0], outs[1])
     rows = torch.cat([torch.arange(0, 300), torch.arange(9400, 9700), torch.arange(T - 300, T), torch.randint(0, T, (400,), generator=g)])
     ref = O.linear_qk_prologue(x[rows], w, gam, bet, cos[rows], sin[rows], norm_mode=mode)
