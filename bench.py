@@ -668,6 +668,68 @@ def bench_div_clamp(dev, rows, hidden, peaks):
             "bytes_equal_torch_on_3_rows": same}
 
 
+def bench_qkv_projection(dev, index, rows, hidden, hq, hkv, peaks, seconds=1.5, iters=None):
+    """get_q + get_k + get_v from the linear on (dit_module.py:953-989) at the workload's token count: three launches of
+    the projection GEMM with the prologue in its epilogue, against the same work as the reference dispatches it - library
+    GEMMs whose bf16 results go to HBM, then the prologue kernel on Q and K.  Tensor-bound; timed back to back for
+    `seconds` (the regime of MEASURED_PEAKS.json's sustained figure) with the SM clock sampled."""
+    import magi_b200 as mb
+    from magi_b200 import host
+    g = torch.Generator(device=dev).manual_seed(12)
+    x = torch.randn(rows, hidden, generator=g, device=dev).to(torch.bfloat16)
+    ws = [(torch.randn(h * 128, hidden, generator=g, device=dev) * hidden ** -0.5).to(torch.bfloat16) for h in (hq, hkv, hkv)]
+    gq, bq, gk, bk = [t.to(dev) for t in host.synthetic_norm_params(12)]
+    cos = torch.rand(rows, 48, generator=g, device=dev)
+    sin = torch.rand(rows, 48, generator=g, device=dev)
+    outs = [torch.empty(rows, h, 128, dtype=torch.bfloat16, device=dev) for h in (hq, hkv, hkv)]
+    ys = [torch.empty(rows, h * 128, dtype=torch.bfloat16, device=dev) for h in (hq, hkv, hkv)]
+    flops = 2.0 * rows * hidden * (hq + 2 * hkv) * 128
+
+    def fused():
+        mb.linear_qk_norm_rope(x, ws[0], gq, bq, cos, sin, out=outs[0])
+        mb.linear_qk_norm_rope(x, ws[1], gk, bk, cos, sin, out=outs[1])
+        mb.linear_qk_norm_rope(x, ws[2], None, None, None, None, norm_mode="none", out=outs[2])
+
+    def unfused():
+        for i in range(3):
+            torch.matmul(x, ws[i].t(), out=ys[i])
+        mb.qk_norm_rope(ys[0].view(rows, hq, 128), gq, bq, cos, sin, out=outs[0])
+        mb.qk_norm_rope(ys[1].view(rows, hkv, 128), gk, bk, cos, sin, out=outs[1])
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        n_it = iters or max(5, int(seconds * 1e3 / a.elapsed_time(b)))
+        sampler = ClockSampler(index)
+        sampler.start()
+        a.record()
+        for _ in range(n_it):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        sampler.stop_flag = True
+        sampler.join()
+        return a.elapsed_time(b) / n_it, sampler.summary()
+
+    ms_u, clk_u = timed(unfused)
+    ref_rows = torch.tensor([0, rows // 2, rows - 1], device=dev)
+    ref = [o[ref_rows].float().clone() for o in outs]
+    ms_f, clk_f = timed(fused)
+    err = max(float((o[ref_rows].float() - r).abs().max()) for o, r in zip(outs, ref))
+    tf = flops / (ms_f * 1e-3) / 1e12
+    return {"kernel": "linear_prologue_kernel", "bound": "tensor", "rows": rows, "in_features": hidden, "heads": [hq, hkv, hkv],
+            "ms": ms_f, "flops": flops, "achieved_tflops": tf, "peak_tflops": peaks["bf16_sustained"], "frac": tf / peaks["bf16_sustained"],
+            "peak": "sustained bf16 (back-to-back launches, %s)" % (f"{iters} steps" if iters else f"{seconds} s"), "clocks": clk_f,
+            "library_gemm_then_prologue_ms": ms_u, "library_gemm_then_prologue_clocks": clk_u,
+            "max_abs_vs_library_gemm_then_prologue_on_3_rows": err, "launches": 3}
+
+
 def flash_child(wname):
     """Child process of the default 1-GPU run: the reference's fallback dispatch on this GPU - a loop of flash_attn_func
     over the ranges (inference/model/dit/dit_module.py:1049-1065) with the flash-attn build of the image - on the same
@@ -729,6 +791,9 @@ def main():
                     help="N > 1: Ulysses exchange fused into the kernels over peer memory, or NCCL all-to-all + copies")
     ap.add_argument("--modulate-only", type=int, default=0, metavar="ROWS",
                     help="time only the gated post-norm residual kernel on ROWS rows of the workload's hidden size and print its block")
+    ap.add_argument("--projection-only", action="store_true",
+                    help="time only the Q/K/V projection with the prologue in its epilogue at the workload's shape (--steps launches of each "
+                         "form, back to back) and print its block")
     ap.add_argument("--flash-child", default=None, help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.flash_child:
@@ -738,6 +803,11 @@ def main():
     if args.modulate_only:
         torch.cuda.set_device(0)
         print(json.dumps(bench_modulate(torch.device("cuda", 0), args.modulate_only, w["hq"] * 128, w["n_chunks"], load_peaks())), flush=True)
+        return
+    if args.projection_only:
+        torch.cuda.set_device(0)
+        C_ = w["H"] * w["W"] * w["frames_per_chunk"]
+        print(json.dumps(bench_qkv_projection(torch.device("cuda", 0), 0, w["n_chunks"] * C_, w["hq"] * 128, w["hq"], w["hkv"], load_peaks(), iters=args.steps)), flush=True)
         return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -801,6 +871,9 @@ def main():
                                                          w["n_chunks"], load_peaks())
         torch.cuda.empty_cache()
         line["fp8_linear_quantiser"] = bench_div_clamp(torch.device("cuda", local_rank), w["n_chunks"] * C_, w["hq"] * 128, load_peaks())
+        torch.cuda.empty_cache()
+        line["qkv_projection_prologue"] = bench_qkv_projection(torch.device("cuda", local_rank), local_rank, w["n_chunks"] * C_, w["hq"] * 128,
+                                                               w["hq"], w["hkv"], load_peaks())
         torch.cuda.empty_cache()
 
     # ---- 1-GPU default run only: the other BASELINE configurations, a few steps each, and the reference's fallback

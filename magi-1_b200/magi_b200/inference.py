@@ -299,3 +299,17 @@ class ChunkCausalSelfAttention:
         query = self.get_q(xq, cos_emb, sin_emb)
         cache, prefix = self.adjust_key_and_value_for_inference(key, xv, inference_params, meta_args)
         return self.core_attention(query, key, xv, meta_args, cache, prefix, proj_in)
+
+    def forward_from_hidden(self, mixed_qqkv: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor,
+                            inference_params: Optional[InferenceParams], rotary_pos_emb: torch.Tensor,
+                            meta_args: ModelMetaArgs, proj_in: Optional[ProjInput] = None) -> torch.Tensor:
+        """The same layer from one step earlier: mixed_qqkv [(sq b), hidden] bf16 is the output of linear_qkv.forward_ln,
+        wq / wk / wv the bf16 torch.nn.Linear weights of linear_qkv.q / .k / .v (dit_module.py:406-408).  The three
+        projections run with the prologue in their epilogue (get_q / get_k / get_v, :953-989, one kernel each): the
+        projections' bf16 outputs never go to HBM."""
+        sin_emb, cos_emb = rotary_pos_emb.tensor_split(2, -1)
+        key = ops.linear_qk_norm_rope(mixed_qqkv, wk, self.k_gamma, self.k_beta, cos_emb, sin_emb, self.eps, self.norm_mode)
+        value = ops.linear_qk_norm_rope(mixed_qqkv, wv, None, None, None, None, norm_mode="none")
+        query = ops.linear_qk_norm_rope(mixed_qqkv, wq, self.q_gamma, self.q_beta, cos_emb, sin_emb, self.eps, self.norm_mode)
+        cache, prefix = self.adjust_key_and_value_for_inference(key, value, inference_params, meta_args)
+        return self.core_attention(query, key, value, meta_args, cache, prefix, proj_in)

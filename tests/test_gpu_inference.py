@@ -161,3 +161,43 @@ def test_host_tier_spill_and_prefetch_round_trip():
         k_page, v_page = cache.read(layer, 0)
         assert torch.equal(k_page, pages[(layer, 0)][0]) and torch.equal(v_page, pages[(layer, 0)][1])
     cache.close()
+
+
+def test_layer_from_hidden_states_matches_layer_from_projections():
+    """forward_from_hidden (projection + prologue in one kernel) against forward on the library GEMM's outputs, through a
+    cached step: the same pages, the same attention; only the GEMM's accumulation order differs."""
+    import magi_b200 as mb
+    from magi_b200 import host
+    from magi_b200.inference import ChunkCausalSelfAttention, InferenceParams, ModelMetaArgs, PackedCoreAttnParams
+    params = host.synthetic_norm_params(62)
+    hidden, n = 384, 2
+    g = torch.Generator().manual_seed(62)
+    wq, wk, wv = [(torch.randn(h * 128, hidden, generator=g) * hidden ** -0.5).to(torch.bfloat16).cuda() for h in (HQ, HKV, HKV)]
+    sin, cos = O.rope_table(6, 10, 13)
+    outs = []
+    for fused in (False, True):
+        layer = ChunkCausalSelfAttention(0, HQ, HKV, *params)
+        ip = InferenceParams(max_batch_size=1, max_sequence_length=3 * C, n_layers=1)
+        gen = torch.Generator().manual_seed(63)
+        res = []
+        for slice_point, k_chunks, update in ((0, [(0, 1)], True), (1, [(0, 2), (0, 3)], False)):
+            nn = len(k_chunks)
+            x = (torch.randn(nn * C, hidden, generator=gen) * 1.5).to(torch.bfloat16).cuda()
+            rows = slice(slice_point * C, (slice_point + nn) * C)
+            rope = torch.cat([sin[rows], cos[rows]], dim=-1).cuda()
+            kr = np.array([[a * C, b * C] for a, b in k_chunks], dtype=np.int32)
+            meta = ModelMetaArgs(slice_point=slice_point, denoising_range_num=nn, clip_token_nums=C,
+                                 core_attn_params=PackedCoreAttnParams.from_numpy(O.consecutive_q_ranges(nn, C), kr, "cuda"),
+                                 fwd_extra_1st_chunk=(slice_point == 0))
+            ip.update_kv_cache = update
+            if fused:
+                res.append(layer.forward_from_hidden(x, wq, wk, wv, ip, rope, meta).clone())
+            else:
+                res.append(layer.forward((x @ wq.t()).view(-1, HQ, 128), (x @ wk.t()).view(-1, HKV, 128),
+                                         (x @ wv.t()).view(-1, HKV, 128), ip, rope, meta).clone())
+            torch.cuda.synchronize()
+            assert mb.Context.get().status() == 0
+        ip.cache.close()
+        outs.append(res)
+    for a, b in zip(*outs):
+        assert_close(b, a, max_abs=4e-2, min_cos=0.9999, what="layer from hidden states")

@@ -95,8 +95,20 @@ def _worker(rank, world, port, mode):
                 return mb.chunk_attn(q_loc, yk, yv, ql, kl, max_q, max(caps), return_lse=False)[0]
         kw["cross_attn_func"] = cross
 
+    x_in = (xq[sl].to(dev), xk[sl].to(dev), xv[sl].to(dev))
+    if mode.get("from_hidden"):
+        # the projections run inside the exchange: hidden states and weights in, the oracle gets the exactly rounded
+        # projections (the GEMM's accumulation order is the only difference)
+        hidden = 256
+        xh = (torch.randn(S, hidden, generator=g) * 1.5).to(torch.bfloat16)
+        ws = [(torch.randn(h * 128, hidden, generator=g) * hidden ** -0.5).to(torch.bfloat16) for h in (Hq, Hkv, Hkv)]
+        xq, xk, xv = [(xh.double() @ w_.double().t()).to(torch.bfloat16).view(S, -1, 128) for w_ in ws]
+        q_ref = O.qk_prologue(xq, gq, bq, cos, sin).float()
+        k_ref = O.qk_prologue(xk, gk, bk, cos, sin).float()
+        x_in = (xh[sl].to(dev), None, None)
+        kw["proj_weights"] = tuple(w_.to(dev) for w_ in ws)
     for _ in range(3):  # later passes reuse (and rotate) the buffers
-        res = ua.forward(xq[sl].to(dev), xk[sl].to(dev), xv[sl].to(dev), gq, bq, gk, bk, cos[sl], sin[sl],
+        res = ua.forward(*x_in, gq, bq, gk, bk, cos[sl], sin[sl],
                          torch.as_tensor(qr, device=dev), torch.as_tensor(kr, device=dev), C, S, **kw)
     out, x_out = res if xattn else (res, None)
     torch.cuda.synchronize()
@@ -160,6 +172,11 @@ def test_fused_exchange_writes_the_projection_operand_with_the_cross_attention_s
     """attn_linear_proj's cat + rearrange (dit_module.py:1332-1346) folded into the fused output exchange; the
     cross-attention fills its half from the schedule's slot (context_parallel.py:584-591)."""
     _spawn(2, fused=True, proj=True, xattn=True)
+
+
+def test_fused_exchange_from_hidden_states():
+    """Projection GEMM -> prologue -> head exchange in one kernel per projection (peer stores from the GEMM's epilogue)."""
+    _spawn(2, fused=True, from_hidden=True)
 
 
 def test_fused_exchange_with_a_head_sharded_paged_prefix():
