@@ -115,7 +115,9 @@ MAGI_API int magi_head_block_copy(magi_ctx* ctx, const magi_prologue_params* p, 
  * epilogue.  Replaces FullyParallelAttention.get_q / get_k / get_v including the linear they start with
  * (inference/model/dit/dit_module.py:953-963 with linear_qkv.forward_q :415-416; :970-980 with forward_k
  * :421-422; :987-989 with forward_v :424-425), for the bf16 torch.nn.Linear case of CustomLayerNormLinear
- * (:406-408; the FP8 linears of the middle layers keep the separate quantiser + library GEMM + prologue).
+ * (:406-408), and - with dtype MAGI_DTYPE_FP8_E4M3 - for its PerTensorQuantizedFp8Linear members (:409-410, forward
+ * :445-456): x is then the e4m3 output of magi_div_clamp_to_e4m3, w the e4m3 weight [out_features, in_features], and
+ * x_scale / w_scale what the reference hands to bmm_fp8 (input_scale, weight_scale; applied as scalars, as bmm_fp8 does).
  * One call per projection.  norm_mode MAGI_NORM_NONE = plain linear (get_v): gamma, beta, cos, sin ignored.
  * The linear's result is rounded to bf16 before the norm, as the reference's Linear output is, and never
  * reaches HBM.  in_features must be a multiple of 128; rot_pairs one of 0, 32, 48, 64.  Destination
@@ -140,6 +142,9 @@ typedef struct {
                                 + t*out_stride_t + (h % heads_per_block)*out_stride_h + d         */
   int64_t out_stride_t, out_stride_h, out_stride_block;
   void* const* out_block_ptrs; /* optional HOST array of H / heads_per_block device pointers (at most 16) */
+  int32_t dtype;             /* operands: MAGI_DTYPE_BF16, or MAGI_DTYPE_FP8_E4M3 (x and w both e4m3, strides in elements) */
+  const float* x_scale;      /* e4m3 only: DEVICE pointers to one fp32 each; the fp32 accumulator is multiplied by          */
+  const float* w_scale;      /* x_scale[0] * w_scale[0] before the bf16 rounding (NULL = 1)                                 */
 } magi_linear_prologue_params;
 MAGI_API int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_prologue_params* p, void* stream);
 

@@ -72,6 +72,8 @@ struct LinearPrologueKernelParams {
   __nv_bfloat16* out_blocks[16];
   int tiles_m, tiles_n;
   int* status;
+  const float* x_scale;  // e4m3 operands: the accumulator is multiplied by x_scale[0] * w_scale[0] (null: 1)
+  const float* w_scale;
 };
 
 // One head of one token: 128 fp32 accumulators in registers -> bf16 rounding of the linear's output -> norm -> rotary
@@ -79,9 +81,9 @@ struct LinearPrologueKernelParams {
 // that every register index is static.
 template <int kRot>
 __device__ __forceinline__ void head_epilogue(float (&v)[kHeadDim], uint32_t (&o)[kHeadDim / 2], const LinearPrologueKernelParams& p,
-                                              const float* g_sh, const float* b_sh, int64_t token, bool row_valid) {
+                                              const float* g_sh, const float* b_sh, int64_t token, bool row_valid, float acc_scale) {
 #pragma unroll
-  for (int c = 0; c < kHeadDim; ++c) v[c] = __bfloat162float(__float2bfloat16_rn(v[c]));
+  for (int c = 0; c < kHeadDim; ++c) v[c] = __bfloat162float(__float2bfloat16_rn(v[c] * acc_scale));
   if (p.norm_mode >= 0) {
     float rstd;
     if (p.norm_mode == MAGI_NORM_LAYERNORM_1P) {
@@ -136,9 +138,9 @@ __device__ __forceinline__ void head_epilogue(float (&v)[kHeadDim], uint32_t (&o
 // 128-byte pieces of a row (eight lanes per row, four rows per instruction); 16-byte chunks XOR-swizzled by the row.
 template <int kRot>
 __device__ __forceinline__ void store_head(float (&v)[kHeadDim], const LinearPrologueKernelParams& p, const float* g_sh,
-                                           const float* b_sh, uint8_t* stage_sh, int head, int row0, int lane) {
+                                           const float* b_sh, uint8_t* stage_sh, int head, int row0, int lane, float acc_scale) {
   uint32_t o[kHeadDim / 2];
-  head_epilogue<kRot>(v, o, p, g_sh, b_sh, (int64_t)row0 + lane, row0 + lane < p.T);
+  head_epilogue<kRot>(v, o, p, g_sh, b_sh, (int64_t)row0 + lane, row0 + lane < p.T, acc_scale);
   // destination of (token, head): block of heads, then the row inside it
   const int blk = p.heads_per_block > 0 ? head / p.heads_per_block : 0;
   const int hs = p.heads_per_block > 0 ? head - blk * p.heads_per_block : head;
@@ -163,7 +165,7 @@ __device__ __forceinline__ void store_head(float (&v)[kHeadDim], const LinearPro
   }
 }
 
-template <bool kPair, int kRot>
+template <bool kPair, int kRot, bool kFp8>
 __global__ void __launch_bounds__(kLpThreads, 1)
 linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                        const LinearPrologueKernelParams p) {
@@ -235,8 +237,9 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
           if (use > 0) ok = kPair ? mbar_wait_cluster(&empty[stage], (use & 1) ^ 1, abort_flag) : mbar_wait(&empty[stage], (use & 1) ^ 1, abort_flag);
           if (!ok) break;
           uint8_t* dst = ring + stage * L::kStageBytes;
-          // x and W are seen as [rows, K / 128, 128]: k-block kb is the half (kb & 1) of 128-column group kb >> 1
-          const int c0 = (kb & 1) * kLpKBlock, c1 = kb >> 1;
+          // x and W are seen as [rows, K / 128, 128]: a k-block is one 128-byte swizzle row per row of the operand, i.e.
+          // 64 bf16 (the half kb & 1 of 128-column group kb >> 1) or 128 e4m3 (group kb)
+          const int c0 = kFp8 ? 0 : (kb & 1) * kLpKBlock, c1 = kFp8 ? kb : kb >> 1;
           if constexpr (kPair) {
             // both CTAs' loads of a stage count on the EVEN CTA's barrier, which its producer arms for both
             if (rank == 0) mbar_expect_tx(&full[stage], 2 * L::kStageBytes);
@@ -259,7 +262,7 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       bool ok = true;
       if (!(kPair && rank == 1)) {
         // ---------------------------------------------------------------- UMMA issuer
-        constexpr uint32_t idesc = umma_idesc(kTileRows, kLpTileN, 1, 1, 0, 0);
+        constexpr uint32_t idesc = kFp8 ? umma_idesc(kTileRows, kLpTileN, 0, 0, 0, 0) : umma_idesc(kTileRows, kLpTileN, 1, 1, 0, 0);
         constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO = 1024 B, version 1, 128-byte swizzle
         const uint32_t ring_lo = (smem_u32(ring) >> 4) | (1u << 16);         // K-major: LBO field = 1
         const uint32_t empty_1 = kPair ? mapa_u32(&empty[0], 1) : 0, acc_full_1 = kPair ? mapa_u32(&acc_full[0], 1) : 0;
@@ -278,18 +281,33 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
             tc_fence_after_sync();
             const uint32_t a_lo = ring_lo + stage * (L::kStageBytes >> 4);
             const uint32_t b_lo = a_lo + (kLpSlab >> 4);
+            // four instructions per k-block: 16 bf16 or 32 e4m3 k-elements = 32 bytes of the swizzle row each
             if constexpr (kPair) {
-              if (kb == 0) umma_ss_f16_lh_pair<0>(d, a_lo, b_lo, desc_hi, idesc);
-              else umma_ss_f16_lh_pair<1>(d, a_lo, b_lo, desc_hi, idesc);
+              if constexpr (kFp8) {
+                if (kb == 0) umma_ss_f8_lh_pair<0>(d, a_lo, b_lo, desc_hi, idesc);
+                else umma_ss_f8_lh_pair<1>(d, a_lo, b_lo, desc_hi, idesc);
 #pragma unroll
-              for (int k = 1; k < 4; ++k) umma_ss_f16_lh_pair<1>(d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);  // 16 k-elements = 32 bytes
+                for (int k = 1; k < 4; ++k) umma_ss_f8_lh_pair<1>(d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+              } else {
+                if (kb == 0) umma_ss_f16_lh_pair<0>(d, a_lo, b_lo, desc_hi, idesc);
+                else umma_ss_f16_lh_pair<1>(d, a_lo, b_lo, desc_hi, idesc);
+#pragma unroll
+                for (int k = 1; k < 4; ++k) umma_ss_f16_lh_pair<1>(d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+              }
               umma_commit_pair(&empty[stage]);
               umma_commit_pair_at(empty_1 + stage * 8);
             } else {
-              if (kb == 0) umma_ss_f16_lh<0>(d, a_lo, b_lo, desc_hi, idesc);
-              else umma_ss_f16_lh<1>(d, a_lo, b_lo, desc_hi, idesc);
+              if constexpr (kFp8) {
+                if (kb == 0) umma_ss_f8_lh<0>(d, a_lo, b_lo, desc_hi, idesc);
+                else umma_ss_f8_lh<1>(d, a_lo, b_lo, desc_hi, idesc);
 #pragma unroll
-              for (int k = 1; k < 4; ++k) umma_ss_f16_lh<1>(d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+                for (int k = 1; k < 4; ++k) umma_ss_f8_lh<1>(d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+              } else {
+                if (kb == 0) umma_ss_f16_lh<0>(d, a_lo, b_lo, desc_hi, idesc);
+                else umma_ss_f16_lh<1>(d, a_lo, b_lo, desc_hi, idesc);
+#pragma unroll
+                for (int k = 1; k < 4; ++k) umma_ss_f16_lh<1>(d, a_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+              }
               umma_commit(&empty[stage]);
             }
           }
@@ -313,6 +331,7 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     uint8_t* stage_sh = smem + L::kStore + ew * 4096;
     const uint32_t acc_empty_0 = kPair ? mapa_u32(&acc_empty[0], 0) : 0;  // the issuer's barriers
+    const float acc_scale = (p.x_scale ? __ldg(p.x_scale) : 1.0f) * (p.w_scale ? __ldg(p.w_scale) : 1.0f);
     bool ok = !*abort_flag;
     int t_local = 0;
     for (int tile = unit; tile < n_tiles && ok; tile += n_units, ++t_local) {
@@ -334,7 +353,7 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
         else mbar_arrive(&acc_empty[a]);
       }
       if (head < p.H)  // warp-uniform: an odd head count leaves half of the last channel block empty
-        store_head<kRot>(v, p, g_sh, b_sh, stage_sh, head, row0, lane);
+        store_head<kRot>(v, p, g_sh, b_sh, stage_sh, head, row0, lane, acc_scale);
     }
   }
 
@@ -350,11 +369,11 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
 }
 
 // ---------------------------------------------------------------------------------------------- host side
-template <bool kPair, int kRot>
+template <bool kPair, int kRot, bool kFp8>
 static int launch_lp(magi_ctx* ctx, const CUtensorMap& tx, const CUtensorMap& tw, const LinearPrologueKernelParams& k, cudaStream_t st) {
   static bool configured[64] = {};  // per device: opt in to > 48 KB of dynamic shared memory once
   if (ctx->device < 64 && !configured[ctx->device]) {
-    MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(linear_prologue_kernel<kPair, kRot>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(linear_prologue_kernel<kPair, kRot, kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            SmemLp<kPair>::kDynamic));
     configured[ctx->device] = true;
   }
@@ -373,18 +392,18 @@ static int launch_lp(magi_ctx* ctx, const CUtensorMap& tx, const CUtensorMap& tw
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  MAGI_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, linear_prologue_kernel<kPair, kRot>, tx, tw, k));
+  MAGI_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, linear_prologue_kernel<kPair, kRot, kFp8>, tx, tw, k));
   return MAGI_OK;
 }
 
-template <bool kPair>
+template <bool kPair, bool kFp8>
 static int launch_lp_rot(magi_ctx* ctx, int rot, const CUtensorMap& tx, const CUtensorMap& tw, const LinearPrologueKernelParams& k,
                          cudaStream_t st) {
   switch (rot) {
-    case 0: return launch_lp<kPair, 0>(ctx, tx, tw, k, st);
-    case 32: return launch_lp<kPair, 32>(ctx, tx, tw, k, st);
-    case 48: return launch_lp<kPair, 48>(ctx, tx, tw, k, st);
-    case 64: return launch_lp<kPair, 64>(ctx, tx, tw, k, st);
+    case 0: return launch_lp<kPair, 0, kFp8>(ctx, tx, tw, k, st);
+    case 32: return launch_lp<kPair, 32, kFp8>(ctx, tx, tw, k, st);
+    case 48: return launch_lp<kPair, 48, kFp8>(ctx, tx, tw, k, st);
+    case 64: return launch_lp<kPair, 64, kFp8>(ctx, tx, tw, k, st);
   }
   return set_err(ctx, MAGI_E_BADARG, "linear prologue: rot_pairs must be 0, 32, 48 or 64 (the reference uses 48)");
 }
@@ -398,6 +417,9 @@ extern "C" int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_pro
   if (!p->x || !p->w || (!p->out && !p->out_block_ptrs) || p->T < 0 || p->H <= 0 || p->in_features <= 0)
     return set_err(ctx, MAGI_E_BADARG, "linear prologue: null tensor or bad shape");
   if (p->in_features % 128) return set_err(ctx, MAGI_E_BADARG, "linear prologue: in_features must be a multiple of 128");
+  if (p->dtype != MAGI_DTYPE_BF16 && p->dtype != MAGI_DTYPE_FP8_E4M3) return set_err(ctx, MAGI_E_BADARG, "linear prologue: dtype is bf16 or e4m3");
+  const bool fp8 = p->dtype == MAGI_DTYPE_FP8_E4M3;
+  const int esz = fp8 ? 1 : 2;
   const bool plain = p->norm_mode == MAGI_NORM_NONE;
   if (!plain && p->norm_mode != MAGI_NORM_LAYERNORM_1P && p->norm_mode != MAGI_NORM_RMSNORM_1P)
     return set_err(ctx, MAGI_E_BADARG, "linear prologue: unknown norm_mode %d", p->norm_mode);
@@ -422,13 +444,15 @@ extern "C" int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_pro
   cudaGetDevice(&prev);
   if (prev != ctx->device) cudaSetDevice(ctx->device);
   CUtensorMap tx, tw;
-  int rc = make_tile_map(ctx, &tx, p->x, p->x_stride, 128, p->T, p->in_features / 128, 2, "linear prologue x");
-  if (!rc) rc = make_tile_map(ctx, &tw, p->w, p->w_stride, 128, p->H * kHeadDim, p->in_features / 128, 2, "linear prologue w");
+  int rc = make_tile_map(ctx, &tx, p->x, p->x_stride, 128, p->T, p->in_features / 128, esz, "linear prologue x");
+  if (!rc) rc = make_tile_map(ctx, &tw, p->w, p->w_stride, 128, p->H * kHeadDim, p->in_features / 128, esz, "linear prologue w");
   if (!rc) {
     LinearPrologueKernelParams k;
     k.T = p->T;
     k.H = p->H;
-    k.k_blocks = p->in_features / kLpKBlock;
+    k.k_blocks = fp8 ? p->in_features / 128 : p->in_features / kLpKBlock;
+    k.x_scale = fp8 ? p->x_scale : nullptr;
+    k.w_scale = fp8 ? p->w_scale : nullptr;
     k.norm_mode = plain ? -1 : p->norm_mode;
     k.eps = p->eps;
     k.gamma = p->gamma;
@@ -452,7 +476,8 @@ extern "C" int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_pro
     const bool pair = force ? force[0] == 'p' : tiles256 >= ctx->sm_count / 2;
     k.tiles_m = pair ? (p->T + 255) / 256 : (p->T + 127) / 128;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    rc = pair ? launch_lp_rot<true>(ctx, rot, tx, tw, k, st) : launch_lp_rot<false>(ctx, rot, tx, tw, k, st);
+    if (fp8) rc = pair ? launch_lp_rot<true, true>(ctx, rot, tx, tw, k, st) : launch_lp_rot<false, true>(ctx, rot, tx, tw, k, st);
+    else rc = pair ? launch_lp_rot<true, false>(ctx, rot, tx, tw, k, st) : launch_lp_rot<false, false>(ctx, rot, tx, tw, k, st);
   }
   if (prev != ctx->device) cudaSetDevice(prev);
   return rc;

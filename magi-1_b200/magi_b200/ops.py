@@ -123,14 +123,18 @@ def qk_norm_rope(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tens
 def linear_qk_norm_rope(x: torch.Tensor, weight: torch.Tensor, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor],
                         cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], eps: float = 1e-6,
                         norm_mode: str = "layernorm_1p", out: Optional[torch.Tensor] = None, heads_per_block: int = 0,
-                        stream=None, block_out=None) -> torch.Tensor:
+                        stream=None, block_out=None, x_scale: Optional[torch.Tensor] = None,
+                        w_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """get_q / get_k / get_v from the projection on (dit_module.py:953-963, :970-980, :987-989), one kernel:
     x bf16 [T, in_features] (the output of forward_ln), weight bf16 [H*128, in_features] (torch.nn.Linear.weight of
     linear_qkv.q / .k / .v) -> bf16 [T, H, 128] = prologue(bf16(x @ weight^T)).  norm_mode "none" is get_v.
-    Destination (out, heads_per_block, block_out) as qk_norm_rope."""
+    With x and weight in float8_e4m3fn (x from div_clamp_to, the weight of a PerTensorQuantizedFp8Linear) the fp32
+    accumulator is multiplied by x_scale[0] * w_scale[0] (CUDA fp32 tensors: input_scale and weight_scale, applied as
+    bmm_fp8 applies them) before the bf16 rounding.  Destination (out, heads_per_block, block_out) as qk_norm_rope."""
+    fp8 = x.dtype == torch.float8_e4m3fn
     for t, name in ((x, "x"), (weight, "weight")):
-        if t.dtype != torch.bfloat16 or not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
-            raise ValueError(f"{name} must be a CUDA bf16 matrix with a contiguous last dim")
+        if t.dtype != (torch.float8_e4m3fn if fp8 else torch.bfloat16) or not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+            raise ValueError(f"{name} must be a CUDA bf16 (or, both, float8_e4m3fn) matrix with a contiguous last dim")
     T, K = x.shape
     if weight.shape[1] != K or weight.shape[0] % HEAD_DIM:
         raise ValueError("weight must be [H*128, in_features]")
@@ -156,6 +160,10 @@ def linear_qk_norm_rope(x: torch.Tensor, weight: torch.Tensor, gamma: Optional[t
             p.rot_pairs, p.cos, p.sin = cos.shape[1], cos.data_ptr(), sin.data_ptr()
     if T == 0:
         return out
+    if fp8:
+        p.dtype = _lib.DTYPE_FP8_E4M3
+        scales = [None if t is None else t.to(device=x.device, dtype=torch.float32).reshape(-1) for t in (x_scale, w_scale)]
+        p.x_scale, p.w_scale = [None if t is None else t.data_ptr() for t in scales]
     keep = _fill_out(p, out, T, H, heads_per_block, block_out)
     check(lib.magi_linear_qk_norm_rope_fwd(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
     KERNEL_LAUNCHES[0] += 1

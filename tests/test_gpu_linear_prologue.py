@@ -114,3 +114,33 @@ def test_bad_arguments_are_refused_on_the_host(mb):
     with pytest.raises(mb.MagiError, match="rot_pairs"):
         mb.linear_qk_norm_rope(x, w, gam, bet, torch.zeros(64, 40), torch.zeros(64, 40))
     assert mb.linear_qk_norm_rope(x[:0], w, gam, bet, None, None).shape == (0, 1, 128)
+
+
+@pytest.mark.parametrize("form", ["solo", "pair"])
+def test_fp8_projection_against_oracle_and_library_gemm(mb, form, monkeypatch):
+    """The middle layers' PerTensorQuantizedFp8Linear members (dit_module.py:409-410, :445-456) in front of get_q: the
+    byte-exact quantiser's e4m3 output and the e4m3 weight go through the same kernel with kind::f8f6f4 UMMAs; sums of
+    e4m3 products are exact in fp32 far beyond this K, so only the bf16 rounding of the scaled accumulator can differ."""
+    from magi_b200 import inference as inf
+    g = torch.Generator().manual_seed(41)
+    T, K, H = 19000, 1024, 8
+    x = (torch.randn(T, K, generator=g) * 2).to(torch.bfloat16)
+    w8 = (torch.randn(H * 128, K, generator=g) * 20).to(torch.float8_e4m3fn)
+    in_scale, w_scale = torch.full((K,), 0.02), torch.tensor([0.003])
+    gam, bet, _, _ = O.make_norm_params(7)
+    sin, cos = O.rope_table(8, 25, 95)
+    xd, wd = x.cuda(), w8.cuda()
+    x8 = mb.div_clamp_to(xd, in_scale)
+    monkeypatch.setenv("MAGI_LINEAR_FORM", form)
+    out = mb.linear_qk_norm_rope(x8, wd, gam, bet, cos, sin, x_scale=in_scale[:1].cuda(), w_scale=w_scale.cuda())
+    torch.cuda.synchronize()
+    assert mb.Context.get().status() == 0
+    rows = torch.cat([torch.arange(0, 200), torch.arange(T - 200, T), torch.randint(0, T, (300,), generator=g)])
+    y_ref = O.fp8_linear(x[rows], in_scale, w8, 0.02, 0.003).to(torch.bfloat16).view(-1, H, 128)
+    ref = O.qk_prologue(y_ref, gam, bet, cos[rows], sin[rows])
+    assert_close(out[rows.cuda()], ref, max_abs=MAX_ABS, min_cos=MIN_COS, what=f"fp8 fused {form}")
+    # the unfused CUDA path: quantiser, library FP8 GEMM, prologue kernel
+    lin = inf.PerTensorQuantizedFp8Linear(wd.unsqueeze(0), w_scale, in_scale)
+    unfused = mb.qk_norm_rope(lin(xd).view(T, H, 128), gam, bet, cos, sin)
+    torch.cuda.synchronize()
+    assert_close(out, unfused, max_abs=MAX_ABS, min_cos=MIN_COS, what=f"fp8 fused vs unfused {form}")
