@@ -717,17 +717,47 @@ def bench_qkv_projection(dev, index, rows, hidden, hq, hkv, peaks, seconds=1.5, 
         sampler.join()
         return a.elapsed_time(b) / n_it, sampler.summary()
 
+    # the same three projections as the middle layers run them (PerTensorQuantizedFp8Linear, dit_module.py:409-410):
+    # activation quantiser, then e4m3 GEMMs; fused = quantiser + this kernel with e4m3 operands, library = quantiser +
+    # torch._scaled_mm (cuBLASLt) + prologue kernel
+    in_scale = torch.full((hidden,), 0.02, device=dev)
+    w8 = [(w_ * 300).to(torch.float8_e4m3fn) for w_ in ws]
+    sa, sb = in_scale[:1].clone(), torch.tensor([1 / 300.0], device=dev)
+    x8 = torch.empty(rows, hidden, dtype=torch.float8_e4m3fn, device=dev)
+
+    def fused8():
+        mb.div_clamp_to(x, in_scale, out=x8)
+        mb.linear_qk_norm_rope(x8, w8[0], gq, bq, cos, sin, out=outs[0], x_scale=sa, w_scale=sb)
+        mb.linear_qk_norm_rope(x8, w8[1], gk, bk, cos, sin, out=outs[1], x_scale=sa, w_scale=sb)
+        mb.linear_qk_norm_rope(x8, w8[2], None, None, None, None, norm_mode="none", out=outs[2], x_scale=sa, w_scale=sb)
+
+    def unfused8():
+        mb.div_clamp_to(x, in_scale, out=x8)
+        for i in range(3):
+            ys[i].copy_(torch._scaled_mm(x8, w8[i].t(), scale_a=sa.reshape(()), scale_b=sb.reshape(()), out_dtype=torch.bfloat16))
+        mb.qk_norm_rope(ys[0].view(rows, hq, 128), gq, bq, cos, sin, out=outs[0])
+        mb.qk_norm_rope(ys[1].view(rows, hkv, 128), gk, bk, cos, sin, out=outs[1])
+
+    seconds_full, seconds = seconds, seconds / 3
+    ms_u8, _ = timed(unfused8)
+    ref8 = outs[0][:4].float().clone()
+    ms_f8, clk_f8 = timed(fused8)
+    err8 = float((outs[0][:4].float() - ref8).abs().max())
+    seconds = seconds_full
     ms_u, clk_u = timed(unfused)
     ref_rows = torch.tensor([0, rows // 2, rows - 1], device=dev)
-    ref = [o[ref_rows].float().clone() for o in outs]
+    ref = [outs[0][ref_rows].float().clone(), outs[1][ref_rows].float().clone(), ys[2].view(rows, hkv, 128)[ref_rows].float().clone()]
     ms_f, clk_f = timed(fused)
-    err = max(float((o[ref_rows].float() - r).abs().max()) for o, r in zip(outs, ref))
+    err = float(torch.stack([(o[ref_rows].float() - r).abs().max() for o, r in zip(outs, ref)]).max())
     tf = flops / (ms_f * 1e-3) / 1e12
     return {"kernel": "linear_prologue_kernel", "bound": "tensor", "rows": rows, "in_features": hidden, "heads": [hq, hkv, hkv],
             "ms": ms_f, "flops": flops, "achieved_tflops": tf, "peak_tflops": peaks["bf16_sustained"], "frac": tf / peaks["bf16_sustained"],
             "peak": "sustained bf16 (back-to-back launches, %s)" % (f"{iters} steps" if iters else f"{seconds} s"), "clocks": clk_f,
             "library_gemm_then_prologue_ms": ms_u, "library_gemm_then_prologue_clocks": clk_u,
-            "max_abs_vs_library_gemm_then_prologue_on_3_rows": err, "launches": 3}
+            "max_abs_vs_library_gemm_then_prologue_on_3_rows": err, "launches": 3,
+            "e4m3_operands": {"what": "activation quantiser + the three projections with e4m3 x and W (the middle layers' FP8 linears)",
+                              "ms": ms_f8, "achieved_tflops": flops / (ms_f8 * 1e-3) / 1e12, "clocks": clk_f8,
+                              "quantiser_library_fp8_gemm_then_prologue_ms": ms_u8, "max_abs_vs_that_on_4_rows": err8, "launches": 4}}
 
 
 def flash_child(wname):
