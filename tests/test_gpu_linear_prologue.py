@@ -144,3 +144,28 @@ def test_fp8_projection_against_oracle_and_library_gemm(mb, form, monkeypatch):
     unfused = mb.qk_norm_rope(lin(xd).view(T, H, 128), gam, bet, cos, sin)
     torch.cuda.synchronize()
     assert_close(out, unfused, max_abs=MAX_ABS, min_cos=MIN_COS, what=f"fp8 fused vs unfused {form}")
+
+
+def test_small_shapes_and_block_pointers(mb):
+    """One ragged row tile with a single head and the smallest K (two k-blocks in bf16, one in e4m3), and the per-block
+    destination pointers the fused Ulysses exchange uses (here two local buffers instead of two ranks' receive buffers)."""
+    g = torch.Generator().manual_seed(43)
+    gam, bet, _, _ = O.make_norm_params(8)
+    for T, K, H in ((5, 128, 1), (129, 128, 2), (300, 256, 4)):
+        x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+        w = (torch.randn(H * 128, K, generator=g) * K ** -0.5).to(torch.bfloat16)
+        cos, sin = torch.rand(T, 48, generator=g), torch.rand(T, 48, generator=g)
+        ref = O.linear_qk_prologue(x, w, gam, bet, cos, sin)
+        out = mb.linear_qk_norm_rope(x.cuda(), w.cuda(), gam, bet, cos, sin)
+        assert_close(out, ref, max_abs=MAX_ABS, min_cos=MIN_COS, what=f"T {T} K {K} H {H}")
+        x8, w8 = (x.float() * 4).to(torch.float8_e4m3fn), (w.float() * 64).to(torch.float8_e4m3fn)
+        y = ((x8.float() @ w8.float().t()) * (0.25 / 64)).to(torch.bfloat16).view(T, H, 128)
+        out8 = mb.linear_qk_norm_rope(x8.cuda(), w8.cuda(), gam, bet, cos, sin, x_scale=torch.tensor([0.25]), w_scale=torch.tensor([1 / 64.]))
+        assert_close(out8, O.qk_prologue(y, gam, bet, cos, sin), max_abs=MAX_ABS, min_cos=MIN_COS, what=f"e4m3 T {T} K {K} H {H}")
+        if H % 2 == 0:
+            bufs = [torch.zeros(T + 3, H // 2, 128, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+            mb.linear_qk_norm_rope(x.cuda(), w.cuda(), gam, bet, cos, sin, heads_per_block=H // 2,
+                                   block_out=([b[3:].data_ptr() for b in bufs], bufs[0].stride(0), bufs[0].stride(1)))
+            torch.cuda.synchronize()
+            assert torch.equal(torch.cat([b[3:] for b in bufs], dim=1), out) and all(float(b[:3].abs().max()) == 0 for b in bufs)
+    assert mb.Context.get().status() == 0
