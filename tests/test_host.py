@@ -188,7 +188,7 @@ def test_flex_attn_accepts_the_reference_call_site():
     import inspect
     import os
     import pytest
-    path = "/root/reference/inference/model/dit/dit_module.py"
+    path = os.path.join(os.environ.get("MAGI_REFERENCE_ROOT", "/root/reference"), "inference/model/dit/dit_module.py")
     if not os.path.exists(path):
         pytest.skip("reference checkout not present")
     import magi_b200
