@@ -118,7 +118,7 @@ MAGI_API int magi_head_block_copy(magi_ctx* ctx, const magi_prologue_params* p, 
  * (:406-408), and - with dtype MAGI_DTYPE_FP8_E4M3 - for its PerTensorQuantizedFp8Linear members (:409-410, forward
  * :445-456): x is then the e4m3 output of magi_div_clamp_to_e4m3, w the e4m3 weight [out_features, in_features], and
  * x_scale / w_scale what the reference hands to bmm_fp8 (input_scale, weight_scale; applied as scalars, as bmm_fp8 does).
- * One call per projection.  norm_mode MAGI_NORM_NONE = plain linear (get_v): gamma, beta, cos, sin ignored.
+ * norm_mode MAGI_NORM_NONE = plain linear (get_v): gamma, beta, cos, sin ignored.
  * The linear's result is rounded to bf16 before the norm, as the reference's Linear output is, and never
  * reaches HBM.  in_features must be a multiple of 128; rot_pairs one of 0, 32, 48, 64.  Destination
  * addressing (blocks of heads, optional per-block base pointers, peer-mapped or not) as magi_prologue_params.
@@ -147,6 +147,12 @@ typedef struct {
   const float* w_scale;      /* x_scale[0] * w_scale[0] before the bf16 rounding (NULL = 1)                                 */
 } magi_linear_prologue_params;
 MAGI_API int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_prologue_params* p, void* stream);
+/* Up to three projections of the same x in ONE launch (FullyParallelAttention.get_qkv / get_kv,
+ * inference/model/dit/dit_module.py:991-1003): `projections` is an array of n (1..3) structs, each with its own w, H,
+ * norm_mode, gamma, beta, w_scale and destination; x, x_stride, T, in_features, dtype, x_scale and eps must be the same in
+ * all of them, and the projections that are rotated share rot_pairs, cos and sin.  Every row block of x is then fetched
+ * from HBM once for all of Q, K and V. */
+MAGI_API int magi_linear_qkv_norm_rope_fwd(magi_ctx* ctx, const magi_linear_prologue_params* projections, int n, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------
  * Chunk-paged KV cache.  Replaces Attention._allocate_key_and_value_memory

@@ -1,5 +1,5 @@
 // Q / K / V projection with the per-head prologue in the GEMM's epilogue, for sm_100a.
-// Replaces, in one kernel per projection, FullyParallelAttention.get_q / get_k / get_v
+// Replaces, in one kernel for one, two or all three projections (get_qkv, :998-1003), FullyParallelAttention.get_q / get_k / get_v
 // (inference/model/dit/dit_module.py:953-963, :970-980, :987-989):
 //     y   = bf16( x @ W^T )                       linear_qkv.forward_q / forward_k / forward_v (:415-425), torch.nn.Linear, no bias
 //     out = bf16( rope( layer_norm_1p( float(y) ) ) )   per (token, head) over the 128 channels of the head; V: out = y
@@ -51,29 +51,37 @@ struct SmemLp {
   static constexpr int kBar = kStore + 8 * 4096;
   static constexpr int kNumBars = 2 * kStages + 4;               // full, empty, acc_full[2], acc_empty[2]
   static constexpr int kMisc = kBar + kNumBars * 8;              // tmem slot, abort flag
-  static constexpr int kGamma = kMisc + 16;                      // float (gamma + 1)[128], beta[128]
-  static constexpr int kTotal = kGamma + 1024;
+  static constexpr int kTotal = kMisc + 16;
   static constexpr int kDynamic = kTotal + 1024;                 // slack to align the base to 1024 bytes
 };
 static_assert(SmemLp<false>::kDynamic <= 232448 && SmemLp<true>::kDynamic <= 232448, "shared memory per CTA");
 
-struct LinearPrologueKernelParams {
-  int T, H, k_blocks;
-  int norm_mode;  // -1: plain linear
-  float eps;
-  const float* gamma;
-  const float* beta;
-  const float* cos;
-  const float* sin;
-  __nv_bfloat16* out;
-  int64_t out_stride_t, out_stride_h, out_stride_block;
+constexpr int kLpMaxSegs = 3;
+
+// One projection of a launch (Q, K or V): its own weight, norm parameters and destination.
+struct LpSegment {
+  int H;
+  int norm_mode;   // -1: plain linear
+  int tile_begin;  // first channel block (two heads) of this projection among the launch's channel blocks
   int heads_per_block;  // 0: no blocking
   int use_block_ptrs;
+  const float* gamma;
+  const float* beta;
+  const float* w_scale;  // e4m3 operands: the accumulator is multiplied by x_scale[0] * w_scale[0] (null: 1)
+  __nv_bfloat16* out;
+  int64_t out_stride_t, out_stride_h, out_stride_block;
   __nv_bfloat16* out_blocks[16];
+};
+
+struct LinearPrologueKernelParams {
+  int T, k_blocks, n_segs;
+  float eps;
+  const float* cos;
+  const float* sin;
+  const float* x_scale;
   int tiles_m, tiles_n;
   int* status;
-  const float* x_scale;  // e4m3 operands: the accumulator is multiplied by x_scale[0] * w_scale[0] (null: 1)
-  const float* w_scale;
+  LpSegment seg[kLpMaxSegs];
 };
 
 // One head of one token: 128 fp32 accumulators in registers -> bf16 rounding of the linear's output -> norm -> rotary
@@ -81,12 +89,12 @@ struct LinearPrologueKernelParams {
 // that every register index is static.
 template <int kRot>
 __device__ __forceinline__ void head_epilogue(float (&v)[kHeadDim], uint32_t (&o)[kHeadDim / 2], const LinearPrologueKernelParams& p,
-                                              const float* g_sh, const float* b_sh, int64_t token, bool row_valid, float acc_scale) {
+                                              const LpSegment& sg, int64_t token, bool row_valid, float acc_scale) {
 #pragma unroll
   for (int c = 0; c < kHeadDim; ++c) v[c] = __bfloat162float(__float2bfloat16_rn(v[c] * acc_scale));
-  if (p.norm_mode >= 0) {
+  if (sg.norm_mode >= 0) {
     float rstd;
-    if (p.norm_mode == MAGI_NORM_LAYERNORM_1P) {
+    if (sg.norm_mode == MAGI_NORM_LAYERNORM_1P) {
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
       for (int c = 0; c < kHeadDim; c += 4) { s0 += v[c]; s1 += v[c + 1]; s2 += v[c + 2]; s3 += v[c + 3]; }
@@ -98,8 +106,14 @@ __device__ __forceinline__ void head_epilogue(float (&v)[kHeadDim], uint32_t (&o
         s0 = fmaf(v[c], v[c], s0); s1 = fmaf(v[c + 1], v[c + 1], s1); s2 = fmaf(v[c + 2], v[c + 2], s2); s3 = fmaf(v[c + 3], v[c + 3], s3);
       }
       rstd = rsqrtf(((s0 + s1) + (s2 + s3)) * (1.f / kHeadDim) + p.eps);
+      // gamma and beta: the same address in every lane (one broadcast transaction each, L1-resident)
+      if (sg.beta) {
 #pragma unroll
-      for (int c = 0; c < kHeadDim; ++c) v[c] = v[c] * rstd * g_sh[c] + b_sh[c];  // same address in every lane: a broadcast
+        for (int c = 0; c < kHeadDim; ++c) v[c] = v[c] * rstd * (__ldg(sg.gamma + c) + 1.0f) + __ldg(sg.beta + c);
+      } else {
+#pragma unroll
+        for (int c = 0; c < kHeadDim; ++c) v[c] = v[c] * rstd * (__ldg(sg.gamma + c) + 1.0f);
+      }
     } else {
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
@@ -108,7 +122,7 @@ __device__ __forceinline__ void head_epilogue(float (&v)[kHeadDim], uint32_t (&o
       }
       rstd = rsqrtf(((s0 + s1) + (s2 + s3)) * (1.f / kHeadDim) + p.eps);
 #pragma unroll
-      for (int c = 0; c < kHeadDim; ++c) v[c] = v[c] * rstd * g_sh[c];
+      for (int c = 0; c < kHeadDim; ++c) v[c] = v[c] * rstd * (__ldg(sg.gamma + c) + 1.0f);
     }
     if constexpr (kRot > 0) {
       if (row_valid) {
@@ -137,14 +151,14 @@ __device__ __forceinline__ void head_epilogue(float (&v)[kHeadDim], uint32_t (&o
 // store, staged through 4 KB of shared memory per warp, 64 channels at a time, so that the global stores are whole
 // 128-byte pieces of a row (eight lanes per row, four rows per instruction); 16-byte chunks XOR-swizzled by the row.
 template <int kRot>
-__device__ __forceinline__ void store_head(float (&v)[kHeadDim], const LinearPrologueKernelParams& p, const float* g_sh,
-                                           const float* b_sh, uint8_t* stage_sh, int head, int row0, int lane, float acc_scale) {
+__device__ __forceinline__ void store_head(float (&v)[kHeadDim], const LinearPrologueKernelParams& p, const LpSegment& sg,
+                                           uint8_t* stage_sh, int head, int row0, int lane, float acc_scale) {
   uint32_t o[kHeadDim / 2];
-  head_epilogue<kRot>(v, o, p, g_sh, b_sh, (int64_t)row0 + lane, row0 + lane < p.T, acc_scale);
+  head_epilogue<kRot>(v, o, p, sg, (int64_t)row0 + lane, row0 + lane < p.T, acc_scale);
   // destination of (token, head): block of heads, then the row inside it
-  const int blk = p.heads_per_block > 0 ? head / p.heads_per_block : 0;
-  const int hs = p.heads_per_block > 0 ? head - blk * p.heads_per_block : head;
-  __nv_bfloat16* base = (p.use_block_ptrs ? p.out_blocks[blk] : p.out + blk * p.out_stride_block) + hs * p.out_stride_h;
+  const int blk = sg.heads_per_block > 0 ? head / sg.heads_per_block : 0;
+  const int hs = sg.heads_per_block > 0 ? head - blk * sg.heads_per_block : head;
+  __nv_bfloat16* base = (sg.use_block_ptrs ? sg.out_blocks[blk] : sg.out + blk * sg.out_stride_block) + hs * sg.out_stride_h;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     __syncwarp();
@@ -159,7 +173,7 @@ __device__ __forceinline__ void store_head(float (&v)[kHeadDim], const LinearPro
       const int rr = 4 * i + rsel;
       if (row0 + rr < p.T) {
         const uint4 val = *reinterpret_cast<const uint4*>(stage_sh + rr * 128 + ((l8 ^ (rr & 7)) << 4));
-        *reinterpret_cast<uint4*>(base + (int64_t)(row0 + rr) * p.out_stride_t + half * 64 + l8 * 8) = val;
+        *reinterpret_cast<uint4*>(base + (int64_t)(row0 + rr) * sg.out_stride_t + half * 64 + l8 * 8) = val;
       }
     }
   }
@@ -167,8 +181,9 @@ __device__ __forceinline__ void store_head(float (&v)[kHeadDim], const LinearPro
 
 template <bool kPair, int kRot, bool kFp8>
 __global__ void __launch_bounds__(kLpThreads, 1)
-linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                       const LinearPrologueKernelParams p) {
+linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w0,
+                       const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2,
+                       const __grid_constant__ LinearPrologueKernelParams p) {
   using L = SmemLp<kPair>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -179,8 +194,6 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
   uint64_t* acc_empty = acc_full + 2;         // pair: the even CTA's barrier collects both CTAs' epilogue warps
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
-  float* g_sh = reinterpret_cast<float*>(smem + L::kGamma);
-  float* b_sh = g_sh + kHeadDim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = kPair ? cluster_ctarank() : 0;  // 0: issues the UMMAs
   const int unit = kPair ? blockIdx.x >> 1 : blockIdx.x, n_units = kPair ? gridDim.x >> 1 : gridDim.x;
@@ -197,10 +210,6 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     }
     *abort_flag = 0;
     fence_mbar_init();
-  }
-  if (threadIdx.x < kHeadDim) {
-    g_sh[threadIdx.x] = p.norm_mode >= 0 ? p.gamma[threadIdx.x] + 1.0f : 1.0f;
-    b_sh[threadIdx.x] = (p.norm_mode == MAGI_NORM_LAYERNORM_1P && p.beta) ? p.beta[threadIdx.x] : 0.0f;
   }
   if (warp == 0) {
     // all 512 columns, by each CTA for itself: in a pair both CTAs then hold the same columns at the same address,
@@ -224,13 +233,19 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && !*abort_flag) {
       tma_prefetch_desc(&tm_x);
-      tma_prefetch_desc(&tm_w);
+      tma_prefetch_desc(&tm_w0);
+      if (p.n_segs > 1) tma_prefetch_desc(&tm_w1);
+      if (p.n_segs > 2) tma_prefetch_desc(&tm_w2);
       int fill = 0;
       bool ok = true;
       const uint32_t full_0 = kPair ? mapa_u32(&full[0], 0) : 0;
       for (int tile = unit; tile < n_tiles && ok; tile += n_units) {
         const int row0 = (tile / p.tiles_n) * kTileRows + rank * 128;
-        const int ch0 = (tile % p.tiles_n) * kLpTileN + (kPair ? rank * 128 : 0);
+        // which projection this channel block belongs to, and its first output channel inside that projection's weight
+        const int nt = tile % p.tiles_n;
+        const int sgi = (p.n_segs > 2 && nt >= p.seg[2].tile_begin) ? 2 : (p.n_segs > 1 && nt >= p.seg[1].tile_begin) ? 1 : 0;
+        const CUtensorMap* tm_w = sgi == 0 ? &tm_w0 : sgi == 1 ? &tm_w1 : &tm_w2;
+        const int ch0 = (nt - p.seg[sgi].tile_begin) * kLpTileN + (kPair ? rank * 128 : 0);
         for (int kb = 0; kb < p.k_blocks; ++kb, ++fill) {
           const int stage = fill % L::kStages, use = fill / L::kStages;
           // the stage is free once the UMMAs that read it have completed (in a pair the issuer commits to both CTAs)
@@ -245,12 +260,12 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
             if (rank == 0) mbar_expect_tx(&full[stage], 2 * L::kStageBytes);
             const uint32_t bar = rank == 0 ? smem_u32(&full[stage]) : full_0 + stage * 8;
             tma_load_3d_pair(dst, &tm_x, bar, c0, c1, row0);
-            tma_load_3d_pair(dst + kLpSlab, &tm_w, bar, c0, c1, ch0);
+            tma_load_3d_pair(dst + kLpSlab, tm_w, bar, c0, c1, ch0);
           } else {
             mbar_expect_tx(&full[stage], L::kStageBytes);
             tma_load_3d(dst, &tm_x, &full[stage], c0, c1, row0);
-            tma_load_3d(dst + kLpSlab, &tm_w, &full[stage], c0, c1, ch0);
-            tma_load_3d(dst + 2 * kLpSlab, &tm_w, &full[stage], c0, c1, ch0 + 128);
+            tma_load_3d(dst + kLpSlab, tm_w, &full[stage], c0, c1, ch0);
+            tma_load_3d(dst + 2 * kLpSlab, tm_w, &full[stage], c0, c1, ch0 + 128);
           }
         }
       }
@@ -331,13 +346,16 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     uint8_t* stage_sh = smem + L::kStore + ew * 4096;
     const uint32_t acc_empty_0 = kPair ? mapa_u32(&acc_empty[0], 0) : 0;  // the issuer's barriers
-    const float acc_scale = (p.x_scale ? __ldg(p.x_scale) : 1.0f) * (p.w_scale ? __ldg(p.w_scale) : 1.0f);
+    const float x_scale = p.x_scale ? __ldg(p.x_scale) : 1.0f;
     bool ok = !*abort_flag;
     int t_local = 0;
     for (int tile = unit; tile < n_tiles && ok; tile += n_units, ++t_local) {
       const int a = t_local & 1;
       const int row0 = (tile / p.tiles_n) * kTileRows + rank * 128 + quarter * 32;
-      const int head = (tile % p.tiles_n) * 2 + hh;
+      const int nt = tile % p.tiles_n;
+      const int sgi = (p.n_segs > 2 && nt >= p.seg[2].tile_begin) ? 2 : (p.n_segs > 1 && nt >= p.seg[1].tile_begin) ? 1 : 0;
+      const LpSegment& sg = p.seg[sgi];
+      const int head = (nt - sg.tile_begin) * 2 + hh;  // head inside its projection
       ok = kPair ? mbar_wait_cluster(&acc_full[a], (uint32_t)(t_local >> 1) & 1, abort_flag) : mbar_wait(&acc_full[a], (uint32_t)(t_local >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
@@ -352,8 +370,8 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
         if constexpr (kPair) mbar_arrive_cluster(acc_empty_0 + a * 8);
         else mbar_arrive(&acc_empty[a]);
       }
-      if (head < p.H)  // warp-uniform: an odd head count leaves half of the last channel block empty
-        store_head<kRot>(v, p, g_sh, b_sh, stage_sh, head, row0, lane, acc_scale);
+      if (head < sg.H)  // warp-uniform: an odd head count leaves half of the projection's last channel block empty
+        store_head<kRot>(v, p, sg, stage_sh, head, row0, lane, x_scale * (sg.w_scale ? __ldg(sg.w_scale) : 1.0f));
     }
   }
 
@@ -370,7 +388,7 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
 
 // ---------------------------------------------------------------------------------------------- host side
 template <bool kPair, int kRot, bool kFp8>
-static int launch_lp(magi_ctx* ctx, const CUtensorMap& tx, const CUtensorMap& tw, const LinearPrologueKernelParams& k, cudaStream_t st) {
+static int launch_lp(magi_ctx* ctx, const CUtensorMap& tx, const CUtensorMap* tw, const LinearPrologueKernelParams& k, cudaStream_t st) {
   static bool configured[64] = {};  // per device: opt in to > 48 KB of dynamic shared memory once
   if (ctx->device < 64 && !configured[ctx->device]) {
     MAGI_CUDA_OK(ctx, cudaFuncSetAttribute(linear_prologue_kernel<kPair, kRot, kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -392,12 +410,12 @@ static int launch_lp(magi_ctx* ctx, const CUtensorMap& tx, const CUtensorMap& tw
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  MAGI_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, linear_prologue_kernel<kPair, kRot, kFp8>, tx, tw, k));
+  MAGI_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, linear_prologue_kernel<kPair, kRot, kFp8>, tx, tw[0], tw[1], tw[2], k));
   return MAGI_OK;
 }
 
 template <bool kPair, bool kFp8>
-static int launch_lp_rot(magi_ctx* ctx, int rot, const CUtensorMap& tx, const CUtensorMap& tw, const LinearPrologueKernelParams& k,
+static int launch_lp_rot(magi_ctx* ctx, int rot, const CUtensorMap& tx, const CUtensorMap* tw, const LinearPrologueKernelParams& k,
                          cudaStream_t st) {
   switch (rot) {
     case 0: return launch_lp<kPair, 0, kFp8>(ctx, tx, tw, k, st);
@@ -408,28 +426,13 @@ static int launch_lp_rot(magi_ctx* ctx, int rot, const CUtensorMap& tx, const CU
   return set_err(ctx, MAGI_E_BADARG, "linear prologue: rot_pairs must be 0, 32, 48 or 64 (the reference uses 48)");
 }
 
-}  // namespace magi
-
-extern "C" int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_prologue_params* p, void* stream) {
-  using namespace magi;
-  if (!ctx) return MAGI_E_BADARG;
-  if (!p || p->struct_size != sizeof(magi_linear_prologue_params)) return set_err(ctx, MAGI_E_BADARG, "linear prologue: bad struct_size");
-  if (!p->x || !p->w || (!p->out && !p->out_block_ptrs) || p->T < 0 || p->H <= 0 || p->in_features <= 0)
-    return set_err(ctx, MAGI_E_BADARG, "linear prologue: null tensor or bad shape");
-  if (p->in_features % 128) return set_err(ctx, MAGI_E_BADARG, "linear prologue: in_features must be a multiple of 128");
-  if (p->dtype != MAGI_DTYPE_BF16 && p->dtype != MAGI_DTYPE_FP8_E4M3) return set_err(ctx, MAGI_E_BADARG, "linear prologue: dtype is bf16 or e4m3");
-  const bool fp8 = p->dtype == MAGI_DTYPE_FP8_E4M3;
-  const int esz = fp8 ? 1 : 2;
+// Checks one projection's own fields and fills its segment.
+static int fill_segment(magi_ctx* ctx, const magi_linear_prologue_params* p, LpSegment& sg) {
+  if (!p->w || (!p->out && !p->out_block_ptrs) || p->H <= 0) return set_err(ctx, MAGI_E_BADARG, "linear prologue: null tensor or bad shape");
   const bool plain = p->norm_mode == MAGI_NORM_NONE;
   if (!plain && p->norm_mode != MAGI_NORM_LAYERNORM_1P && p->norm_mode != MAGI_NORM_RMSNORM_1P)
     return set_err(ctx, MAGI_E_BADARG, "linear prologue: unknown norm_mode %d", p->norm_mode);
-  const int rot = plain ? 0 : p->rot_pairs;
-  if (!plain) {
-    if (!p->gamma) return set_err(ctx, MAGI_E_BADARG, "linear prologue: gamma is required");
-    if (rot > 0 && (!p->cos || !p->sin)) return set_err(ctx, MAGI_E_BADARG, "linear prologue: cos/sin required");
-    if (rot > 0 && ((reinterpret_cast<uintptr_t>(p->cos) & 15) || (reinterpret_cast<uintptr_t>(p->sin) & 15)))
-      return set_err(ctx, MAGI_E_ALIGN, "linear prologue: cos/sin must be 16-byte aligned");
-  }
+  if (!plain && !p->gamma) return set_err(ctx, MAGI_E_BADARG, "linear prologue: gamma is required");
   if (p->out_block_ptrs) {
     if (p->heads_per_block <= 0 || p->H % p->heads_per_block || p->H / p->heads_per_block > 16)
       return set_err(ctx, MAGI_E_BADARG, "linear prologue: out_block_ptrs needs heads_per_block dividing H into at most 16 blocks");
@@ -439,35 +442,79 @@ extern "C" int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_pro
   }
   if ((reinterpret_cast<uintptr_t>(p->out) & 15) || (p->out_stride_t & 7) || (p->out_stride_h & 7) || (p->out_stride_block & 7))
     return set_err(ctx, MAGI_E_ALIGN, "linear prologue: out must be 16-byte aligned and its strides multiples of 8 elements");
+  sg.H = p->H;
+  sg.norm_mode = plain ? -1 : p->norm_mode;
+  sg.gamma = p->gamma;
+  sg.beta = (!plain && p->norm_mode == MAGI_NORM_LAYERNORM_1P) ? p->beta : nullptr;
+  sg.w_scale = p->dtype == MAGI_DTYPE_FP8_E4M3 ? p->w_scale : nullptr;
+  sg.out = reinterpret_cast<__nv_bfloat16*>(p->out);
+  sg.out_stride_t = p->out_stride_t;
+  sg.out_stride_h = p->out_stride_h;
+  sg.out_stride_block = p->out_stride_block;
+  sg.heads_per_block = (p->heads_per_block > 0 && (p->heads_per_block < p->H || p->out_block_ptrs)) ? p->heads_per_block : 0;
+  sg.use_block_ptrs = p->out_block_ptrs ? 1 : 0;
+  for (int b = 0; b < 16; ++b)
+    sg.out_blocks[b] = (p->out_block_ptrs && b < p->H / p->heads_per_block) ? reinterpret_cast<__nv_bfloat16*>(p->out_block_ptrs[b]) : nullptr;
+  return MAGI_OK;
+}
+
+}  // namespace magi
+
+extern "C" int magi_linear_qkv_norm_rope_fwd(magi_ctx* ctx, const magi_linear_prologue_params* segs, int n_segs, void* stream) {
+  using namespace magi;
+  if (!ctx) return MAGI_E_BADARG;
+  if (!segs || n_segs < 1 || n_segs > kLpMaxSegs) return set_err(ctx, MAGI_E_BADARG, "linear prologue: 1 to %d projections per call", kLpMaxSegs);
+  const magi_linear_prologue_params* p = &segs[0];
+  for (int i = 0; i < n_segs; ++i)
+    if (segs[i].struct_size != sizeof(magi_linear_prologue_params)) return set_err(ctx, MAGI_E_BADARG, "linear prologue: bad struct_size");
+  if (!p->x || p->T < 0 || p->in_features <= 0) return set_err(ctx, MAGI_E_BADARG, "linear prologue: null tensor or bad shape");
+  if (p->in_features % 128) return set_err(ctx, MAGI_E_BADARG, "linear prologue: in_features must be a multiple of 128");
+  if (p->dtype != MAGI_DTYPE_BF16 && p->dtype != MAGI_DTYPE_FP8_E4M3) return set_err(ctx, MAGI_E_BADARG, "linear prologue: dtype is bf16 or e4m3");
+  const bool fp8 = p->dtype == MAGI_DTYPE_FP8_E4M3;
+  const int esz = fp8 ? 1 : 2;
+  LinearPrologueKernelParams k = {};
+  int rot = 0;
+  for (int i = 0; i < n_segs; ++i) {
+    const magi_linear_prologue_params* q = &segs[i];
+    // the projections of one call share the input: x, its scale, the token count, the rotary table
+    if (q->x != p->x || q->x_stride != p->x_stride || q->T != p->T || q->in_features != p->in_features || q->dtype != p->dtype ||
+        q->x_scale != p->x_scale || q->eps != p->eps)
+      return set_err(ctx, MAGI_E_BADARG, "linear prologue: projection %d does not share x, T, in_features, dtype, x_scale and eps with the first", i);
+    if (int rc = fill_segment(ctx, q, k.seg[i])) return rc;
+    if (q->norm_mode != MAGI_NORM_NONE && q->rot_pairs > 0) {
+      if (!q->cos || !q->sin) return set_err(ctx, MAGI_E_BADARG, "linear prologue: cos/sin required");
+      if ((reinterpret_cast<uintptr_t>(q->cos) & 15) || (reinterpret_cast<uintptr_t>(q->sin) & 15))
+        return set_err(ctx, MAGI_E_ALIGN, "linear prologue: cos/sin must be 16-byte aligned");
+      if (rot && (rot != q->rot_pairs || k.cos != q->cos || k.sin != q->sin))
+        return set_err(ctx, MAGI_E_BADARG, "linear prologue: the rotated projections of one call share rot_pairs, cos and sin");
+      rot = q->rot_pairs;
+      k.cos = q->cos;
+      k.sin = q->sin;
+    } else if (q->norm_mode != MAGI_NORM_NONE && n_segs > 1 && rot == 0) {
+      // a normed projection without rotary beside rotated ones would need a kernel of its own
+      for (int j = 0; j < n_segs; ++j)
+        if (segs[j].norm_mode != MAGI_NORM_NONE && segs[j].rot_pairs > 0)
+          return set_err(ctx, MAGI_E_BADARG, "linear prologue: the normed projections of one call are all rotated or all not");
+    }
+    k.seg[i].tile_begin = k.tiles_n;
+    k.tiles_n += (q->H + 1) / 2;
+  }
   if (p->T == 0) return MAGI_OK;
   int prev = 0;
   cudaGetDevice(&prev);
   if (prev != ctx->device) cudaSetDevice(ctx->device);
-  CUtensorMap tx, tw;
+  CUtensorMap tx, tw[kLpMaxSegs];
   int rc = make_tile_map(ctx, &tx, p->x, p->x_stride, 128, p->T, p->in_features / 128, esz, "linear prologue x");
-  if (!rc) rc = make_tile_map(ctx, &tw, p->w, p->w_stride, 128, p->H * kHeadDim, p->in_features / 128, esz, "linear prologue w");
+  for (int i = 0; i < kLpMaxSegs && !rc; ++i) {
+    const magi_linear_prologue_params* q = &segs[i < n_segs ? i : 0];  // unused maps repeat the first
+    rc = make_tile_map(ctx, &tw[i], q->w, q->w_stride, 128, q->H * kHeadDim, p->in_features / 128, esz, "linear prologue w");
+  }
   if (!rc) {
-    LinearPrologueKernelParams k;
     k.T = p->T;
-    k.H = p->H;
+    k.n_segs = n_segs;
     k.k_blocks = fp8 ? p->in_features / 128 : p->in_features / kLpKBlock;
-    k.x_scale = fp8 ? p->x_scale : nullptr;
-    k.w_scale = fp8 ? p->w_scale : nullptr;
-    k.norm_mode = plain ? -1 : p->norm_mode;
     k.eps = p->eps;
-    k.gamma = p->gamma;
-    k.beta = p->beta;
-    k.cos = p->cos;
-    k.sin = p->sin;
-    k.out = reinterpret_cast<__nv_bfloat16*>(p->out);
-    k.out_stride_t = p->out_stride_t;
-    k.out_stride_h = p->out_stride_h;
-    k.out_stride_block = p->out_stride_block;
-    k.heads_per_block = (p->heads_per_block > 0 && (p->heads_per_block < p->H || p->out_block_ptrs)) ? p->heads_per_block : 0;
-    k.use_block_ptrs = p->out_block_ptrs ? 1 : 0;
-    for (int b = 0; b < 16; ++b)
-      k.out_blocks[b] = (p->out_block_ptrs && b < p->H / p->heads_per_block) ? reinterpret_cast<__nv_bfloat16*>(p->out_block_ptrs[b]) : nullptr;
-    k.tiles_n = (p->H + 1) / 2;
+    k.x_scale = fp8 ? p->x_scale : nullptr;
     k.status = reinterpret_cast<int*>(reinterpret_cast<char*>(ctx->workspace) + offsetof(PlanHeader, status));
     // CTA pairs unless the problem is too small to give every pair a 256-row tile; MAGI_LINEAR_FORM=solo|pair overrides
     // (kept for A/B measurements)
@@ -481,4 +528,8 @@ extern "C" int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_pro
   }
   if (prev != ctx->device) cudaSetDevice(prev);
   return rc;
+}
+
+extern "C" int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_prologue_params* p, void* stream) {
+  return magi_linear_qkv_norm_rope_fwd(ctx, p, p ? 1 : 0, stream);
 }

@@ -19,7 +19,7 @@ EXPORTS = [
     "magi_kv_cache_append", "magi_kv_cache_evict", "magi_kv_cache_read", "magi_kv_cache_bytes",
     "magi_chunk_attn_fwd", "magi_chunk_attn_fwd_simt", "magi_quantize_e4m3_block128", "magi_chunk_attn_fwd_noalloc",
     "magi_peer_alloc", "magi_peer_open", "magi_peer_close", "magi_peer_free", "magi_selftest_bounded_wait",
-    "magi_bias_modulate_add", "magi_div_clamp_to_e4m3", "magi_linear_qk_norm_rope_fwd",
+    "magi_bias_modulate_add", "magi_div_clamp_to_e4m3", "magi_linear_qk_norm_rope_fwd", "magi_linear_qkv_norm_rope_fwd",
     "magi_ulysses_unique_id", "magi_ulysses_create", "magi_ulysses_destroy", "magi_ulysses_a2a_in", "magi_ulysses_a2a_out",
 ]
 
@@ -114,6 +114,7 @@ def _load():
         "magi_qk_norm_rope_fwd": (C.c_int, [vp, C.POINTER(PrologueParams), vp]),
         "magi_head_block_copy": (C.c_int, [vp, C.POINTER(PrologueParams), vp]),
         "magi_linear_qk_norm_rope_fwd": (C.c_int, [vp, C.POINTER(LinearPrologueParams), vp]),
+        "magi_linear_qkv_norm_rope_fwd": (C.c_int, [vp, C.POINTER(LinearPrologueParams), i32, vp]),
         "magi_kv_cache_create": (C.c_int, [vp, C.POINTER(KVCacheDesc), C.POINTER(vp)]),
         "magi_kv_cache_destroy": (C.c_int, [vp]),
         "magi_kv_cache_append": (C.c_int, [vp, i32, i32, vp, i64, i64, vp, i64, i64, i32, i32, vp]),

@@ -305,11 +305,12 @@ class ChunkCausalSelfAttention:
                             meta_args: ModelMetaArgs, proj_in: Optional[ProjInput] = None) -> torch.Tensor:
         """The same layer from one step earlier: mixed_qqkv [(sq b), hidden] bf16 is the output of linear_qkv.forward_ln,
         wq / wk / wv the bf16 torch.nn.Linear weights of linear_qkv.q / .k / .v (dit_module.py:406-408).  The three
-        projections run with the prologue in their epilogue (get_q / get_k / get_v, :953-989, one kernel each): the
-        projections' bf16 outputs never go to HBM."""
+        projections run in one kernel with the prologue in its epilogue (get_qkv, :953-1003): the projections' bf16 outputs
+        never go to HBM and x is read from HBM once."""
         sin_emb, cos_emb = rotary_pos_emb.tensor_split(2, -1)
-        key = ops.linear_qk_norm_rope(mixed_qqkv, wk, self.k_gamma, self.k_beta, cos_emb, sin_emb, self.eps, self.norm_mode)
-        value = ops.linear_qk_norm_rope(mixed_qqkv, wv, None, None, None, None, norm_mode="none")
-        query = ops.linear_qk_norm_rope(mixed_qqkv, wq, self.q_gamma, self.q_beta, cos_emb, sin_emb, self.eps, self.norm_mode)
+        query, key, value = ops.linear_qkv_norm_rope(mixed_qqkv, [
+            dict(weight=wq, gamma=self.q_gamma, beta=self.q_beta, norm_mode=self.norm_mode),
+            dict(weight=wk, gamma=self.k_gamma, beta=self.k_beta, norm_mode=self.norm_mode),
+            dict(weight=wv, norm_mode="none")], cos_emb, sin_emb, self.eps)
         cache, prefix = self.adjust_key_and_value_for_inference(key, value, inference_params, meta_args)
         return self.core_attention(query, key, value, meta_args, cache, prefix, proj_in)

@@ -120,54 +120,84 @@ def qk_norm_rope(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tens
     return out
 
 
+def linear_qkv_norm_rope(x: torch.Tensor, projections, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                         eps: float = 1e-6, stream=None, x_scale: Optional[torch.Tensor] = None):
+    """get_qkv / get_kv / get_q / get_k / get_v from the projection on (dit_module.py:953-1003) in ONE kernel: x
+    [T, in_features] (the output of forward_ln) against one to three weights.
+
+    projections: a list of dicts, one per projection, with the keys
+      weight      [H*128, in_features] (torch.nn.Linear.weight of linear_qkv.q / .k / .v), the same dtype as x
+      gamma, beta the per-head norm's parameters (gamma applied as gamma + 1); not needed with norm_mode "none"
+      norm_mode   "layernorm_1p" (default), "rmsnorm" or "none" (get_v: the projection as it is, no rotary)
+      out, heads_per_block, block_out   destination as qk_norm_rope (default: a new packed [T, H, 128])
+      w_scale     e4m3 operands only: CUDA fp32 tensor, first entry used
+    x and the weights are bf16, or all float8_e4m3fn (x from div_clamp_to, weights of PerTensorQuantizedFp8Linear
+    members): the fp32 accumulator is then multiplied by x_scale[0] * w_scale[0] - input_scale and weight_scale, applied
+    as bmm_fp8 applies them - before the bf16 rounding.  Returns the list of outputs (None where block_out was given)."""
+    fp8 = x.dtype == torch.float8_e4m3fn
+    want = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    if x.dtype != want or not x.is_cuda or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be a CUDA bf16 or float8_e4m3fn matrix with a contiguous last dim")
+    if not 1 <= len(projections) <= 3:
+        raise ValueError("one to three projections per call")
+    T, K = x.shape
+    ctx = Context.get(x.device)
+    arr = (LinearPrologueParams * len(projections))()
+    keep, outs = [], []
+    if cos is not None:
+        cos = cos.to(device=x.device, dtype=torch.float32).contiguous()
+        sin = sin.to(device=x.device, dtype=torch.float32).contiguous()
+        assert cos.shape == sin.shape and cos.shape[0] == T
+    xs = None if x_scale is None else x_scale.to(device=x.device, dtype=torch.float32).reshape(-1)
+    for p, pr in zip(arr, projections):
+        w = pr["weight"]
+        if w.dtype != want or not w.is_cuda or w.dim() != 2 or w.stride(1) != 1 or w.shape[1] != K or w.shape[0] % HEAD_DIM:
+            raise ValueError("weight must be a CUDA [H*128, in_features] matrix of x's dtype with a contiguous last dim")
+        H = w.shape[0] // HEAD_DIM
+        mode = pr.get("norm_mode", "layernorm_1p")
+        out, block_out = pr.get("out"), pr.get("block_out")
+        if out is None and block_out is None:
+            out = torch.empty(T, H, HEAD_DIM, dtype=torch.bfloat16, device=x.device)
+        p.struct_size = C.sizeof(LinearPrologueParams)
+        p.norm_mode = {"layernorm_1p": _lib.NORM_LAYERNORM_1P, "rmsnorm": _lib.NORM_RMSNORM_1P, "none": _lib.NORM_NONE}[mode]
+        p.x, p.x_stride, p.w, p.w_stride, p.T, p.H, p.in_features = x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), T, H, K
+        p.eps = eps
+        if mode != "none":
+            gamma = pr["gamma"].to(device=x.device, dtype=torch.float32).contiguous()
+            p.gamma = gamma.data_ptr()
+            keep.append(gamma)
+            if pr.get("beta") is not None:
+                beta = pr["beta"].to(device=x.device, dtype=torch.float32).contiguous()
+                p.beta = beta.data_ptr()
+                keep.append(beta)
+            if cos is not None:
+                p.rot_pairs, p.cos, p.sin = cos.shape[1], cos.data_ptr(), sin.data_ptr()
+        if fp8:
+            p.dtype = _lib.DTYPE_FP8_E4M3
+            p.x_scale = None if xs is None else xs.data_ptr()
+            if pr.get("w_scale") is not None:
+                ws = pr["w_scale"].to(device=x.device, dtype=torch.float32).reshape(-1)
+                p.w_scale = ws.data_ptr()
+                keep.append(ws)
+        if T > 0:
+            keep.append(_fill_out(p, out, T, H, pr.get("heads_per_block", 0), block_out))
+        outs.append(out)
+    if T > 0:
+        check(lib.magi_linear_qkv_norm_rope_fwd(ctx.handle, arr, len(projections), _stream(stream)), ctx.handle)
+        KERNEL_LAUNCHES[0] += 1
+    return outs
+
+
 def linear_qk_norm_rope(x: torch.Tensor, weight: torch.Tensor, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor],
                         cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], eps: float = 1e-6,
                         norm_mode: str = "layernorm_1p", out: Optional[torch.Tensor] = None, heads_per_block: int = 0,
                         stream=None, block_out=None, x_scale: Optional[torch.Tensor] = None,
                         w_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """get_q / get_k / get_v from the projection on (dit_module.py:953-963, :970-980, :987-989), one kernel:
-    x bf16 [T, in_features] (the output of forward_ln), weight bf16 [H*128, in_features] (torch.nn.Linear.weight of
-    linear_qkv.q / .k / .v) -> bf16 [T, H, 128] = prologue(bf16(x @ weight^T)).  norm_mode "none" is get_v.
-    With x and weight in float8_e4m3fn (x from div_clamp_to, the weight of a PerTensorQuantizedFp8Linear) the fp32
-    accumulator is multiplied by x_scale[0] * w_scale[0] (CUDA fp32 tensors: input_scale and weight_scale, applied as
-    bmm_fp8 applies them) before the bf16 rounding.  Destination (out, heads_per_block, block_out) as qk_norm_rope."""
-    fp8 = x.dtype == torch.float8_e4m3fn
-    for t, name in ((x, "x"), (weight, "weight")):
-        if t.dtype != (torch.float8_e4m3fn if fp8 else torch.bfloat16) or not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
-            raise ValueError(f"{name} must be a CUDA bf16 (or, both, float8_e4m3fn) matrix with a contiguous last dim")
-    T, K = x.shape
-    if weight.shape[1] != K or weight.shape[0] % HEAD_DIM:
-        raise ValueError("weight must be [H*128, in_features]")
-    H = weight.shape[0] // HEAD_DIM
-    ctx = Context.get(x.device)
-    if out is None and block_out is None:
-        out = torch.empty(T, H, HEAD_DIM, dtype=torch.bfloat16, device=x.device)
-    p = LinearPrologueParams()
-    p.struct_size = C.sizeof(LinearPrologueParams)
-    p.norm_mode = {"layernorm_1p": _lib.NORM_LAYERNORM_1P, "rmsnorm": _lib.NORM_RMSNORM_1P, "none": _lib.NORM_NONE}[norm_mode]
-    p.x, p.x_stride, p.w, p.w_stride, p.T, p.H, p.in_features = x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), T, H, K
-    p.eps = eps
-    if norm_mode != "none":
-        gamma = gamma.to(device=x.device, dtype=torch.float32).contiguous()
-        p.gamma = gamma.data_ptr()
-        if beta is not None:
-            beta = beta.to(device=x.device, dtype=torch.float32).contiguous()
-            p.beta = beta.data_ptr()
-        if cos is not None:
-            cos = cos.to(device=x.device, dtype=torch.float32).contiguous()
-            sin = sin.to(device=x.device, dtype=torch.float32).contiguous()
-            assert cos.shape == sin.shape and cos.shape[0] == T
-            p.rot_pairs, p.cos, p.sin = cos.shape[1], cos.data_ptr(), sin.data_ptr()
-    if T == 0:
-        return out
-    if fp8:
-        p.dtype = _lib.DTYPE_FP8_E4M3
-        scales = [None if t is None else t.to(device=x.device, dtype=torch.float32).reshape(-1) for t in (x_scale, w_scale)]
-        p.x_scale, p.w_scale = [None if t is None else t.data_ptr() for t in scales]
-    keep = _fill_out(p, out, T, H, heads_per_block, block_out)
-    check(lib.magi_linear_qk_norm_rope_fwd(ctx.handle, C.byref(p), _stream(stream)), ctx.handle)
-    KERNEL_LAUNCHES[0] += 1
-    return out
+    """One projection (get_q, get_k or get_v, dit_module.py:953-989) through linear_qkv_norm_rope: x [T, in_features],
+    weight [H*128, in_features] -> bf16 [T, H, 128] = prologue(bf16(x @ weight^T)); norm_mode "none" is get_v."""
+    return linear_qkv_norm_rope(x, [dict(weight=weight, gamma=gamma, beta=beta, norm_mode=norm_mode, out=out,
+                                         heads_per_block=heads_per_block, block_out=block_out, w_scale=w_scale)],
+                                cos, sin, eps, stream, x_scale)[0]
 
 
 def head_block_copy(x: torch.Tensor, out: Optional[torch.Tensor], heads_per_block: int = 0, stream=None, block_out=None

@@ -344,7 +344,7 @@ class FusedUlyssesAttention:
                 fp8_chunk_tokens: int = 0, kv_current_offset: int = 0, cross_attn_func=None, proj_weights=None):
         """Arguments as UlyssesAttention.forward.  proj_weights = (wq, wk, wv), the bf16 torch.nn.Linear weights of
         linear_qkv.q / .k / .v (dit_module.py:406-408): xq is then this rank's hidden states [s_local, hidden] (the output
-        of forward_ln), xk / xv are ignored, and each projection runs as one kernel with the prologue and the head
+        of forward_ln), xk / xv are ignored, and the three projections run as one kernel with the prologue and the head
         exchange in its epilogue.  cache / prefix_chunk_ids: a head-sharded paged prefix (the cache holds
         this rank's Hkv/cp heads, dit_module.py:794-798); the k ranges then address (prefix pages | current tokens).
         kv_current_offset: the received K/V from this token on are the "current" keys (earlier tokens, if any, are
@@ -366,13 +366,14 @@ class FusedUlyssesAttention:
         v_dst = [p + (off * kv_row + HEAD_DIM) * 2 for p in self.peer_kv]
         q_dst = [p + off * q_row * 2 for p in self.peer_q]
         if proj_weights is not None:
-            # projection GEMM -> prologue -> "scatter heads" exchange in ONE kernel per projection: the GEMM's epilogue
-            # stores each rank's heads straight into that rank's receive buffer
+            # projection GEMMs -> prologue -> "scatter heads" exchange in ONE kernel: the GEMM's epilogue stores each
+            # rank's heads of Q, K and V straight into that rank's receive buffers
             wq, wk, wv = proj_weights
-            ops.linear_qk_norm_rope(xq, wk, gk, bk, cos, sin, eps, norm_mode, heads_per_block=self.hkv_loc, block_out=(k_dst, kv_row, 2 * HEAD_DIM))
-            ops.linear_qk_norm_rope(xq, wv, None, None, None, None, norm_mode="none", heads_per_block=self.hkv_loc,
-                                    block_out=(v_dst, kv_row, 2 * HEAD_DIM))
-            ops.linear_qk_norm_rope(xq, wq, gq, bq, cos, sin, eps, norm_mode, heads_per_block=self.hq_loc, block_out=(q_dst, q_row, HEAD_DIM))
+            ops.linear_qkv_norm_rope(xq, [
+                dict(weight=wk, gamma=gk, beta=bk, norm_mode=norm_mode, heads_per_block=self.hkv_loc, block_out=(k_dst, kv_row, 2 * HEAD_DIM)),
+                dict(weight=wv, norm_mode="none", heads_per_block=self.hkv_loc, block_out=(v_dst, kv_row, 2 * HEAD_DIM)),
+                dict(weight=wq, gamma=gq, beta=bq, norm_mode=norm_mode, heads_per_block=self.hq_loc, block_out=(q_dst, q_row, HEAD_DIM))],
+                cos, sin, eps)
         else:
             ops.qk_norm_rope(xk, gk, bk, cos, sin, eps, norm_mode, heads_per_block=self.hkv_loc, block_out=(k_dst, kv_row, 2 * HEAD_DIM))
             ops.head_block_copy(xv, None, heads_per_block=self.hkv_loc, block_out=(v_dst, kv_row, 2 * HEAD_DIM))

@@ -169,3 +169,28 @@ def test_small_shapes_and_block_pointers(mb):
             torch.cuda.synchronize()
             assert torch.equal(torch.cat([b[3:] for b in bufs], dim=1), out) and all(float(b[:3].abs().max()) == 0 for b in bufs)
     assert mb.Context.get().status() == 0
+
+
+@pytest.mark.parametrize("form", ["solo", "pair"])
+def test_q_k_v_in_one_launch_equals_three_launches(mb, form, monkeypatch):
+    """get_qkv (dit_module.py:998-1003): three weights, two norm parameter sets and three destinations in one kernel; odd
+    head counts (each projection's last channel block is half empty) and a K|V fused destination.  Per tile the
+    arithmetic is that of the single-projection launches, so the bytes are the same."""
+    g = torch.Generator().manual_seed(47)
+    T, K, Hq, Hkv = 1500, 512, 5, 3
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).cuda()
+    wq, wk, wv = [(torch.randn(h * 128, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda() for h in (Hq, Hkv, Hkv)]
+    gq, bq, gk, bk = O.make_norm_params(9)
+    cos, sin = torch.rand(T, 48, generator=g), torch.rand(T, 48, generator=g)
+    monkeypatch.setenv("MAGI_LINEAR_FORM", form)
+    kv = torch.zeros(T, Hkv, 256, dtype=torch.bfloat16, device="cuda")
+    q, k, v = mb.linear_qkv_norm_rope(x, [dict(weight=wq, gamma=gq, beta=bq), dict(weight=wk, gamma=gk, beta=bk, out=kv[:, :, :128]),
+                                          dict(weight=wv, norm_mode="none", out=kv[:, :, 128:])], cos, sin)
+    torch.cuda.synchronize()
+    assert mb.Context.get().status() == 0
+    assert torch.equal(q, mb.linear_qk_norm_rope(x, wq, gq, bq, cos, sin))
+    assert torch.equal(kv[:, :, :128], mb.linear_qk_norm_rope(x, wk, gk, bk, cos, sin))
+    assert torch.equal(kv[:, :, 128:], mb.linear_qk_norm_rope(x, wv, None, None, None, None, norm_mode="none"))
+    assert_close(q, O.linear_qk_prologue(x.cpu(), wq.cpu(), gq, bq, cos, sin), max_abs=MAX_ABS, min_cos=MIN_COS, what="q of qkv")
+    with pytest.raises(ValueError):
+        mb.linear_qkv_norm_rope(x, [dict(weight=wq, gamma=gq, beta=bq), dict(weight=wk[:, :256].contiguous(), gamma=gk, beta=bk)], cos, sin)
