@@ -147,11 +147,12 @@ typedef struct {
   const float* w_scale;      /* x_scale[0] * w_scale[0] before the bf16 rounding (NULL = 1)                                 */
 } magi_linear_prologue_params;
 MAGI_API int magi_linear_qk_norm_rope_fwd(magi_ctx* ctx, const magi_linear_prologue_params* p, void* stream);
-/* Up to three projections of the same x in ONE launch (FullyParallelAttention.get_qkv / get_kv,
- * inference/model/dit/dit_module.py:991-1003): `projections` is an array of n (1..3) structs, each with its own w, H,
- * norm_mode, gamma, beta, w_scale and destination; x, x_stride, T, in_features, dtype, x_scale and eps must be the same in
- * all of them, and the projections that are rotated share rot_pairs, cos and sin.  Every row block of x is then fetched
- * from HBM once for all of Q, K and V. */
+/* Up to four projections of the same x in ONE launch - q, qx, k, v, the members of the reference's CustomLayerNormLinear
+ * (inference/model/dit/dit_module.py:404): FullyParallelAttention.get_qkv / get_kv (:991-1003) and the query half of
+ * get_xqkv (:1005-1008: forward_qx, then q_layernorm_xattn, no rotary).  `projections` is an array of n (1..4) structs,
+ * each with its own w, H, norm_mode, gamma, beta, rot_pairs (0 = normed but not rotated), w_scale and destination; x,
+ * x_stride, T, in_features, dtype, x_scale and eps must be the same in all of them, and the projections that are rotated
+ * share rot_pairs, cos and sin.  Every row block of x is then fetched from HBM once for all of them. */
 MAGI_API int magi_linear_qkv_norm_rope_fwd(magi_ctx* ctx, const magi_linear_prologue_params* projections, int n, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------

@@ -56,12 +56,13 @@ struct SmemLp {
 };
 static_assert(SmemLp<false>::kDynamic <= 232448 && SmemLp<true>::kDynamic <= 232448, "shared memory per CTA");
 
-constexpr int kLpMaxSegs = 3;
+constexpr int kLpMaxSegs = 4;  // q, qx, k, v: the four members of the reference's CustomLayerNormLinear
 
 // One projection of a launch (Q, K or V): its own weight, norm parameters and destination.
 struct LpSegment {
   int H;
   int norm_mode;   // -1: plain linear
+  int rotate;      // rotary after the norm (the cross-attention query, qx, is normed but not rotated)
   int tile_begin;  // first channel block (two heads) of this projection among the launch's channel blocks
   int heads_per_block;  // 0: no blocking
   int use_block_ptrs;
@@ -125,7 +126,7 @@ __device__ __forceinline__ void head_epilogue(float (&v)[kHeadDim], uint32_t (&o
       for (int c = 0; c < kHeadDim; ++c) v[c] = v[c] * rstd * (__ldg(sg.gamma + c) + 1.0f);
     }
     if constexpr (kRot > 0) {
-      if (row_valid) {
+      if (row_valid && sg.rotate) {
         const float4* cs = reinterpret_cast<const float4*>(p.cos + token * kRot);
         const float4* sn = reinterpret_cast<const float4*>(p.sin + token * kRot);
 #pragma unroll
@@ -183,7 +184,7 @@ template <bool kPair, int kRot, bool kFp8>
 __global__ void __launch_bounds__(kLpThreads, 1)
 linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w0,
                        const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2,
-                       const __grid_constant__ LinearPrologueKernelParams p) {
+                       const __grid_constant__ CUtensorMap tm_w3, const __grid_constant__ LinearPrologueKernelParams p) {
   using L = SmemLp<kPair>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -236,6 +237,7 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       tma_prefetch_desc(&tm_w0);
       if (p.n_segs > 1) tma_prefetch_desc(&tm_w1);
       if (p.n_segs > 2) tma_prefetch_desc(&tm_w2);
+      if (p.n_segs > 3) tma_prefetch_desc(&tm_w3);
       int fill = 0;
       bool ok = true;
       const uint32_t full_0 = kPair ? mapa_u32(&full[0], 0) : 0;
@@ -243,8 +245,9 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
         const int row0 = (tile / p.tiles_n) * kTileRows + rank * 128;
         // which projection this channel block belongs to, and its first output channel inside that projection's weight
         const int nt = tile % p.tiles_n;
-        const int sgi = (p.n_segs > 2 && nt >= p.seg[2].tile_begin) ? 2 : (p.n_segs > 1 && nt >= p.seg[1].tile_begin) ? 1 : 0;
-        const CUtensorMap* tm_w = sgi == 0 ? &tm_w0 : sgi == 1 ? &tm_w1 : &tm_w2;
+        int sgi = 0;
+        for (int i = 1; i < p.n_segs; ++i) sgi = nt >= p.seg[i].tile_begin ? i : sgi;
+        const CUtensorMap* tm_w = sgi == 0 ? &tm_w0 : sgi == 1 ? &tm_w1 : sgi == 2 ? &tm_w2 : &tm_w3;
         const int ch0 = (nt - p.seg[sgi].tile_begin) * kLpTileN + (kPair ? rank * 128 : 0);
         for (int kb = 0; kb < p.k_blocks; ++kb, ++fill) {
           const int stage = fill % L::kStages, use = fill / L::kStages;
@@ -353,7 +356,8 @@ linear_prologue_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_co
       const int a = t_local & 1;
       const int row0 = (tile / p.tiles_n) * kTileRows + rank * 128 + quarter * 32;
       const int nt = tile % p.tiles_n;
-      const int sgi = (p.n_segs > 2 && nt >= p.seg[2].tile_begin) ? 2 : (p.n_segs > 1 && nt >= p.seg[1].tile_begin) ? 1 : 0;
+      int sgi = 0;
+      for (int i = 1; i < p.n_segs; ++i) sgi = nt >= p.seg[i].tile_begin ? i : sgi;
       const LpSegment& sg = p.seg[sgi];
       const int head = (nt - sg.tile_begin) * 2 + hh;  // head inside its projection
       ok = kPair ? mbar_wait_cluster(&acc_full[a], (uint32_t)(t_local >> 1) & 1, abort_flag) : mbar_wait(&acc_full[a], (uint32_t)(t_local >> 1) & 1, abort_flag);
@@ -410,7 +414,7 @@ static int launch_lp(magi_ctx* ctx, const CUtensorMap& tx, const CUtensorMap* tw
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  MAGI_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, linear_prologue_kernel<kPair, kRot, kFp8>, tx, tw[0], tw[1], tw[2], k));
+  MAGI_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, linear_prologue_kernel<kPair, kRot, kFp8>, tx, tw[0], tw[1], tw[2], tw[3], k));
   return MAGI_OK;
 }
 
@@ -481,6 +485,7 @@ extern "C" int magi_linear_qkv_norm_rope_fwd(magi_ctx* ctx, const magi_linear_pr
         q->x_scale != p->x_scale || q->eps != p->eps)
       return set_err(ctx, MAGI_E_BADARG, "linear prologue: projection %d does not share x, T, in_features, dtype, x_scale and eps with the first", i);
     if (int rc = fill_segment(ctx, q, k.seg[i])) return rc;
+    k.seg[i].rotate = 0;
     if (q->norm_mode != MAGI_NORM_NONE && q->rot_pairs > 0) {
       if (!q->cos || !q->sin) return set_err(ctx, MAGI_E_BADARG, "linear prologue: cos/sin required");
       if ((reinterpret_cast<uintptr_t>(q->cos) & 15) || (reinterpret_cast<uintptr_t>(q->sin) & 15))
@@ -490,11 +495,7 @@ extern "C" int magi_linear_qkv_norm_rope_fwd(magi_ctx* ctx, const magi_linear_pr
       rot = q->rot_pairs;
       k.cos = q->cos;
       k.sin = q->sin;
-    } else if (q->norm_mode != MAGI_NORM_NONE && n_segs > 1 && rot == 0) {
-      // a normed projection without rotary beside rotated ones would need a kernel of its own
-      for (int j = 0; j < n_segs; ++j)
-        if (segs[j].norm_mode != MAGI_NORM_NONE && segs[j].rot_pairs > 0)
-          return set_err(ctx, MAGI_E_BADARG, "linear prologue: the normed projections of one call are all rotated or all not");
+      k.seg[i].rotate = 1;
     }
     k.seg[i].tile_begin = k.tiles_n;
     k.tiles_n += (q->H + 1) / 2;

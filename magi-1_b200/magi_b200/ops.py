@@ -123,12 +123,13 @@ def qk_norm_rope(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tens
 def linear_qkv_norm_rope(x: torch.Tensor, projections, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                          eps: float = 1e-6, stream=None, x_scale: Optional[torch.Tensor] = None):
     """get_qkv / get_kv / get_q / get_k / get_v from the projection on (dit_module.py:953-1003) in ONE kernel: x
-    [T, in_features] (the output of forward_ln) against one to three weights.
+    [T, in_features] (the output of forward_ln) against one to four weights (q, qx, k, v).
 
     projections: a list of dicts, one per projection, with the keys
       weight      [H*128, in_features] (torch.nn.Linear.weight of linear_qkv.q / .k / .v), the same dtype as x
       gamma, beta the per-head norm's parameters (gamma applied as gamma + 1); not needed with norm_mode "none"
       norm_mode   "layernorm_1p" (default), "rmsnorm" or "none" (get_v: the projection as it is, no rotary)
+      rotate      False: normed but not rotated (the cross-attention query of get_xqkv, :1005-1008); default True
       out, heads_per_block, block_out   destination as qk_norm_rope (default: a new packed [T, H, 128])
       w_scale     e4m3 operands only: CUDA fp32 tensor, first entry used
     x and the weights are bf16, or all float8_e4m3fn (x from div_clamp_to, weights of PerTensorQuantizedFp8Linear
@@ -138,8 +139,8 @@ def linear_qkv_norm_rope(x: torch.Tensor, projections, cos: Optional[torch.Tenso
     want = torch.float8_e4m3fn if fp8 else torch.bfloat16
     if x.dtype != want or not x.is_cuda or x.dim() != 2 or x.stride(1) != 1:
         raise ValueError("x must be a CUDA bf16 or float8_e4m3fn matrix with a contiguous last dim")
-    if not 1 <= len(projections) <= 3:
-        raise ValueError("one to three projections per call")
+    if not 1 <= len(projections) <= 4:
+        raise ValueError("one to four projections per call")
     T, K = x.shape
     ctx = Context.get(x.device)
     arr = (LinearPrologueParams * len(projections))()
@@ -170,7 +171,7 @@ def linear_qkv_norm_rope(x: torch.Tensor, projections, cos: Optional[torch.Tenso
                 beta = pr["beta"].to(device=x.device, dtype=torch.float32).contiguous()
                 p.beta = beta.data_ptr()
                 keep.append(beta)
-            if cos is not None:
+            if cos is not None and pr.get("rotate", True):
                 p.rot_pairs, p.cos, p.sin = cos.shape[1], cos.data_ptr(), sin.data_ptr()
         if fp8:
             p.dtype = _lib.DTYPE_FP8_E4M3

@@ -194,3 +194,48 @@ def test_q_k_v_in_one_launch_equals_three_launches(mb, form, monkeypatch):
     assert_close(q, O.linear_qk_prologue(x.cpu(), wq.cpu(), gq, bq, cos, sin), max_abs=MAX_ABS, min_cos=MIN_COS, what="q of qkv")
     with pytest.raises(ValueError):
         mb.linear_qkv_norm_rope(x, [dict(weight=wq, gamma=gq, beta=bq), dict(weight=wk[:, :256].contiguous(), gamma=gk, beta=bk)], cos, sin)
+
+
+def test_all_four_members_of_linear_qkv_in_one_launch(mb):
+    """q, qx, k, v (CustomLayerNormLinear, dit_module.py:404): the cross-attention query qx is normed by its own LayerNorm
+    and NOT rotated (get_xqkv, :1005-1008) while q and k are; one launch against four single-projection launches."""
+    g = torch.Generator().manual_seed(53)
+    T, K, Hq, Hkv = 900, 256, 4, 2
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).cuda()
+    wq, wqx, wk, wv = [(torch.randn(h * 128, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda() for h in (Hq, Hq, Hkv, Hkv)]
+    gq, bq, gk, bk = O.make_norm_params(10)
+    gx, bx, _, _ = O.make_norm_params(11)
+    cos, sin = torch.rand(T, 48, generator=g), torch.rand(T, 48, generator=g)
+    q, qx, k, v = mb.linear_qkv_norm_rope(x, [dict(weight=wq, gamma=gq, beta=bq), dict(weight=wqx, gamma=gx, beta=bx, rotate=False),
+                                              dict(weight=wk, gamma=gk, beta=bk), dict(weight=wv, norm_mode="none")], cos, sin)
+    torch.cuda.synchronize()
+    assert mb.Context.get().status() == 0
+    assert torch.equal(q, mb.linear_qk_norm_rope(x, wq, gq, bq, cos, sin))
+    assert torch.equal(qx, mb.linear_qk_norm_rope(x, wqx, gx, bx, None, None))
+    assert torch.equal(k, mb.linear_qk_norm_rope(x, wk, gk, bk, cos, sin))
+    assert torch.equal(v, mb.linear_qk_norm_rope(x, wv, None, None, None, None, norm_mode="none"))
+    y = O.linear_qk_prologue(x.cpu(), wqx.cpu(), None, None, None, None, norm_mode="none")
+    assert_close(qx, O.layer_norm_1p(y, gx, bx, 1e-6), max_abs=MAX_ABS, min_cos=MIN_COS, what="qx: norm, no rotary")
+
+
+def test_projection_at_the_720p_shape(mb):
+    """86400 tokens x 6144 features -> 48 + 8 + 8 heads in one launch (the shape bench.py times): sampled rows against the
+    oracle (tile and pair edges, the last ragged tile, random rows)."""
+    g = torch.Generator(device="cuda").manual_seed(59)
+    T, K, Hq, Hkv = 86400, 6144, 48, 8
+    x = torch.randn(T, K, generator=g, device="cuda").to(torch.bfloat16)
+    wq, wk, wv = [(torch.randn(h * 128, K, generator=g, device="cuda") * K ** -0.5).to(torch.bfloat16) for h in (Hq, Hkv, Hkv)]
+    gq, bq, gk, bk = O.make_norm_params(12)
+    cos, sin = torch.rand(T, 48, generator=g, device="cuda"), torch.rand(T, 48, generator=g, device="cuda")
+    q, k, v = mb.linear_qkv_norm_rope(x, [dict(weight=wq, gamma=gq, beta=bq), dict(weight=wk, gamma=gk, beta=bk),
+                                          dict(weight=wv, norm_mode="none")], cos, sin)
+    torch.cuda.synchronize()
+    assert mb.Context.get().status() == 0
+    gc = torch.Generator().manual_seed(59)
+    rows = torch.cat([torch.tensor([0, 127, 128, 255, 256, T - 129, T - 128, T - 1]), torch.randint(0, T, (56,), generator=gc)]).cuda()
+    xs, cs, sn = x[rows].cpu(), cos[rows].cpu(), sin[rows].cpu()
+    assert_close(q[rows], O.linear_qk_prologue(xs, wq.cpu(), gq, bq, cs, sn), max_abs=MAX_ABS, min_cos=MIN_COS, what="720p q")
+    assert_close(k[rows], O.linear_qk_prologue(xs, wk.cpu(), gk, bk, cs, sn), max_abs=MAX_ABS, min_cos=MIN_COS, what="720p k")
+    assert_close(v[rows], O.linear_qk_prologue(xs, wv.cpu(), None, None, None, None, norm_mode="none"), max_abs=2 ** -5,
+                 min_cos=MIN_COS, what="720p v")
+    assert torch.isfinite(q.float()).all() and torch.isfinite(k.float()).all()
