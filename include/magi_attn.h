@@ -143,6 +143,9 @@ typedef struct {
   int64_t out_stride_t, out_stride_h, out_stride_block;
   void* const* out_block_ptrs; /* optional HOST array of H / heads_per_block device pointers (at most 16) */
   int32_t dtype;             /* operands: MAGI_DTYPE_BF16, or MAGI_DTYPE_FP8_E4M3 (x and w both e4m3, strides in elements) */
+  int32_t plain_odd_heads;   /* 1: heads 1, 3, 5, ... are plain (no norm, no rotary): the weight of linear_kv_xattn, whose rows are
+                                (k of head 0, v of head 0, k of head 1, ...) so that out [T, 2*Hkv, 128] IS the K|V buffer [T, Hkv, 256]
+                                of get_xqkv (inference/model/dit/dit_module.py:1010-1020) */
   const float* x_scale;      /* e4m3 only: DEVICE pointers to one fp32 each; the fp32 accumulator is multiplied by          */
   const float* w_scale;      /* x_scale[0] * w_scale[0] before the bf16 rounding (NULL = 1)                                 */
 } magi_linear_prologue_params;

@@ -63,6 +63,7 @@ struct LpSegment {
   int H;
   int norm_mode;   // -1: plain linear
   int rotate;      // rotary after the norm (the cross-attention query, qx, is normed but not rotated)
+  int plain_odd;   // heads 1, 3, 5, ... are plain: a K|V-interleaved weight (k of head 0, v of head 0, k of head 1, ...)
   int tile_begin;  // first channel block (two heads) of this projection among the launch's channel blocks
   int heads_per_block;  // 0: no blocking
   int use_block_ptrs;
@@ -90,10 +91,10 @@ struct LinearPrologueKernelParams {
 // that every register index is static.
 template <int kRot>
 __device__ __forceinline__ void head_epilogue(float (&v)[kHeadDim], uint32_t (&o)[kHeadDim / 2], const LinearPrologueKernelParams& p,
-                                              const LpSegment& sg, int64_t token, bool row_valid, float acc_scale) {
+                                              const LpSegment& sg, bool normed, int64_t token, bool row_valid, float acc_scale) {
 #pragma unroll
   for (int c = 0; c < kHeadDim; ++c) v[c] = __bfloat162float(__float2bfloat16_rn(v[c] * acc_scale));
-  if (sg.norm_mode >= 0) {
+  if (normed) {
     float rstd;
     if (sg.norm_mode == MAGI_NORM_LAYERNORM_1P) {
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
@@ -155,7 +156,7 @@ template <int kRot>
 __device__ __forceinline__ void store_head(float (&v)[kHeadDim], const LinearPrologueKernelParams& p, const LpSegment& sg,
                                            uint8_t* stage_sh, int head, int row0, int lane, float acc_scale) {
   uint32_t o[kHeadDim / 2];
-  head_epilogue<kRot>(v, o, p, sg, (int64_t)row0 + lane, row0 + lane < p.T, acc_scale);
+  head_epilogue<kRot>(v, o, p, sg, sg.norm_mode >= 0 && !(sg.plain_odd && (head & 1)), (int64_t)row0 + lane, row0 + lane < p.T, acc_scale);
   // destination of (token, head): block of heads, then the row inside it
   const int blk = sg.heads_per_block > 0 ? head / sg.heads_per_block : 0;
   const int hs = sg.heads_per_block > 0 ? head - blk * sg.heads_per_block : head;
@@ -448,6 +449,7 @@ static int fill_segment(magi_ctx* ctx, const magi_linear_prologue_params* p, LpS
     return set_err(ctx, MAGI_E_ALIGN, "linear prologue: out must be 16-byte aligned and its strides multiples of 8 elements");
   sg.H = p->H;
   sg.norm_mode = plain ? -1 : p->norm_mode;
+  sg.plain_odd = p->plain_odd_heads ? 1 : 0;
   sg.gamma = p->gamma;
   sg.beta = (!plain && p->norm_mode == MAGI_NORM_LAYERNORM_1P) ? p->beta : nullptr;
   sg.w_scale = p->dtype == MAGI_DTYPE_FP8_E4M3 ? p->w_scale : nullptr;

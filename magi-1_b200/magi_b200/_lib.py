@@ -46,7 +46,7 @@ class LinearPrologueParams(C.Structure):
         ("cos", C.c_void_p), ("sin", C.c_void_p),
         ("out", C.c_void_p), ("out_stride_t", C.c_int64), ("out_stride_h", C.c_int64), ("out_stride_block", C.c_int64),
         ("out_block_ptrs", C.POINTER(C.c_void_p)),
-        ("dtype", C.c_int32), ("x_scale", C.c_void_p), ("w_scale", C.c_void_p),
+        ("dtype", C.c_int32), ("plain_odd_heads", C.c_int32), ("x_scale", C.c_void_p), ("w_scale", C.c_void_p),
     ]
 
 

@@ -231,6 +231,20 @@ class PerChannelQuantizedFp8Linear(PerTensorQuantizedFp8Linear):
         return self.smooth_scale
 
 
+def get_xqkv(mixed_qqkv: torch.Tensor, key_value_states: torch.Tensor, wqx: torch.Tensor, w_kv_xattn: torch.Tensor,
+             q_gamma, q_beta, k_gamma, k_beta, eps: float = 1e-6):
+    """FullyParallelAttention.get_xqkv (inference/model/dit/dit_module.py:1005-1021) from the projections on, two kernels:
+    mixed_qqkv [(b sq), hidden] (the output of forward_ln) through linear_qkv.qx and q_layernorm_xattn (no rotary), and the
+    caption states key_value_states [y_total_token, caption_dim] through linear_kv_xattn - whose weight rows are
+    (k of head 0, v of head 0, k of head 1, ...), :1015 - with k_layernorm_xattn on the k halves.  Returns
+    query_xattn [(b sq), Hq, 128], key_xattn and value_xattn [y_total_token, Hkv, 128] (views of one K|V buffer)."""
+    (q,) = ops.linear_qkv_norm_rope(mixed_qqkv, [dict(weight=wqx, gamma=q_gamma, beta=q_beta, rotate=False)], None, None, eps)
+    (kv,) = ops.linear_qkv_norm_rope(key_value_states, [dict(weight=w_kv_xattn, gamma=k_gamma, beta=k_beta, plain_odd_heads=True)],
+                                     None, None, eps)
+    kv = kv.view(kv.shape[0], -1, 2 * ops.HEAD_DIM)
+    return q, kv[..., :ops.HEAD_DIM], kv[..., ops.HEAD_DIM:]
+
+
 class ChunkCausalSelfAttention:
     """One layer's self-attention core: prologue -> KV-cache gate -> chunk-causal attention."""
 

@@ -130,6 +130,9 @@ def linear_qkv_norm_rope(x: torch.Tensor, projections, cos: Optional[torch.Tenso
       gamma, beta the per-head norm's parameters (gamma applied as gamma + 1); not needed with norm_mode "none"
       norm_mode   "layernorm_1p" (default), "rmsnorm" or "none" (get_v: the projection as it is, no rotary)
       rotate      False: normed but not rotated (the cross-attention query of get_xqkv, :1005-1008); default True
+      plain_odd_heads  True: heads 1, 3, 5, ... are left as projected - the weight of linear_kv_xattn, whose rows are
+                  (k of head 0, v of head 0, k of head 1, ...), so that the output [T, 2*Hkv, 128] is the K|V buffer
+                  [T, Hkv, 256] of get_xqkv (:1010-1020)
       out, heads_per_block, block_out   destination as qk_norm_rope (default: a new packed [T, H, 128])
       w_scale     e4m3 operands only: CUDA fp32 tensor, first entry used
     x and the weights are bf16, or all float8_e4m3fn (x from div_clamp_to, weights of PerTensorQuantizedFp8Linear
@@ -163,6 +166,7 @@ def linear_qkv_norm_rope(x: torch.Tensor, projections, cos: Optional[torch.Tenso
         p.norm_mode = {"layernorm_1p": _lib.NORM_LAYERNORM_1P, "rmsnorm": _lib.NORM_RMSNORM_1P, "none": _lib.NORM_NONE}[mode]
         p.x, p.x_stride, p.w, p.w_stride, p.T, p.H, p.in_features = x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), T, H, K
         p.eps = eps
+        p.plain_odd_heads = 1 if pr.get("plain_odd_heads") else 0
         if mode != "none":
             gamma = pr["gamma"].to(device=x.device, dtype=torch.float32).contiguous()
             p.gamma = gamma.data_ptr()

@@ -54,7 +54,7 @@ def test_struct_layouts_match_the_header(tmp_path):
                                  "eps", "gamma_plus_one", "out", "out_stride", "rows", "hidden"],
         "magi_linear_prologue_params": ["x", "x_stride", "w", "w_stride", "T", "H", "in_features", "eps", "gamma", "beta",
                                         "rot_pairs", "heads_per_block", "cos", "sin", "out", "out_stride_t", "out_stride_h",
-                                        "out_stride_block", "out_block_ptrs", "dtype", "x_scale", "w_scale"],
+                                        "out_stride_block", "out_block_ptrs", "dtype", "plain_odd_heads", "x_scale", "w_scale"],
     }
     body = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]
     for s, fs in fields.items():

@@ -48,3 +48,31 @@ def test_cross_attention_shape_and_norm_without_rope():
         o_r, _ = mb.chunk_attn(q_d[offs[r]:offs[r + 1]], k_d, v.cuda(), ql, kl, max_q, 800)
         torch.cuda.synchronize()
         assert torch.equal(o_r, out[offs[r]:offs[r + 1]])
+
+
+def test_get_xqkv_from_hidden_and_caption_states():
+    """get_xqkv (dit_module.py:1005-1021) from the projections on: qx + q_layernorm_xattn (no rotary) and the K|V-interleaved
+    linear_kv_xattn + k_layernorm_xattn, each one kernel, then the caption cross-attention over them against the oracle."""
+    import magi_b200 as mb
+    from magi_b200 import host, inference
+    g = torch.Generator().manual_seed(71)
+    C, n, Hq, Hkv, hidden, cap_dim = 260, 2, 6, 2, 384, 512
+    caps = [77, 130]
+    x = (torch.randn(n * C, hidden, generator=g) * 1.3).to(torch.bfloat16)
+    y = torch.randn(sum(caps), cap_dim, generator=g).to(torch.bfloat16)
+    wqx = (torch.randn(Hq * 128, hidden, generator=g) * hidden ** -0.5).to(torch.bfloat16)
+    wkv = (torch.randn(2 * Hkv * 128, cap_dim, generator=g) * cap_dim ** -0.5).to(torch.bfloat16)
+    gq, bq, gk, bk = O.make_norm_params(71)
+    q, k, v = inference.get_xqkv(x.cuda(), y.cuda(), wqx.cuda(), wkv.cuda(), gq, bq, gk, bk)
+    torch.cuda.synchronize()
+    assert mb.Context.get().status() == 0
+    q_ref, k_ref, v_ref = O.get_xqkv(x, y, wqx, wkv, gq, bq, gk, bk)
+    assert q.shape == q_ref.shape and k.shape == k_ref.shape == (sum(caps), Hkv, 128)
+    assert_close(q, q_ref, max_abs=4e-2, min_cos=0.99999, what="query_xattn")
+    assert_close(k, k_ref, max_abs=4e-2, min_cos=0.99999, what="key_xattn")
+    assert_close(v, v_ref, max_abs=2 ** -5, min_cos=0.99999, what="value_xattn")
+    qr, kr = host.cross_attn_ranges(C, n, caps)
+    out, _ = mb.chunk_attn(q, k, v, qr, kr, C, max(caps), return_lse=False)
+    torch.cuda.synchronize()
+    ref, _ = O.range_attention(q.cpu().float(), k.cpu().float(), v.cpu().float(), qr, as_segments(kr))
+    assert_close(out, ref, what="cross-attention over the fused projections")
