@@ -36,6 +36,10 @@ What is produced (all seeded, small enough to commit):
                  (dit_module.py:390-425, bf16 torch.nn.Linear members) forward_q / forward_k / forward_v on CPU, then
                  the reference's FusedLayerNorm and flash-attn's pure-torch rotary, in get_q's order (:953-963).
 
+  xqkv.npz       FullyParallelAttention.get_xqkv (dit_module.py:1005-1021) called unbound on a namespace that carries the
+                 reference's own CustomLayerNormLinear (forward_qx), torch.nn.Linear linear_kv_xattn and two FusedLayerNorm
+                 modules: the cross-attention query, key and value from hidden states and caption states.
+
 The reference holds no attention fixture of its own; see the oracle's header.
 """
 import argparse
@@ -395,6 +399,31 @@ def gen_linear_prologue(ref_mod, out_dir):
     np.savez_compressed(os.path.join(out_dir, "linear_prologue.npz"), **out)
 
 
+def gen_xqkv(ref_mod, out_dir):
+    g = torch.Generator().manual_seed(29)
+    T, K, Hq, Hkv, D, cap_dim, Y = 72, 128, 2, 1, 128, 128, 40
+    mcfg = types.SimpleNamespace(apply_layernorm_1p=True, layernorm_epsilon=1e-6, params_dtype=torch.bfloat16, num_layers=4)
+    lin = ref_mod.CustomLayerNormLinear(K, Hq * D, Hkv * D, 1, mcfg, types.SimpleNamespace(fp8_quant=False))
+    kv_lin = torch.nn.Linear(cap_dim, 2 * Hkv * D, bias=False, dtype=torch.bfloat16)
+    ncfg = types.SimpleNamespace(apply_layernorm_1p=True, layernorm_epsilon=1e-6, params_dtype=torch.float32)
+    qn, kn = ref_mod.FusedLayerNorm(ncfg, D), ref_mod.FusedLayerNorm(ncfg, D)
+    with torch.no_grad():
+        lin.qx.weight.copy_((torch.randn(Hq * D, K, generator=g) * K ** -0.5).to(torch.bfloat16))
+        kv_lin.weight.copy_((torch.randn(2 * Hkv * D, cap_dim, generator=g) * cap_dim ** -0.5).to(torch.bfloat16))
+        for ln in (qn, kn):
+            ln.weight.copy_(0.1 * torch.randn(D, generator=g))
+            ln.bias.copy_(0.02 * torch.randn(D, generator=g))
+    x = (torch.randn(T, 1, K, generator=g) * 1.3).to(torch.bfloat16)
+    y = torch.randn(Y, cap_dim, generator=g).to(torch.bfloat16)
+    me = types.SimpleNamespace(linear_qkv=lin, q_layernorm_xattn=qn, k_layernorm_xattn=kn, linear_kv_xattn=kv_lin,
+                               hidden_size_per_attention_head=D)
+    with torch.no_grad():
+        q, k, v = ref_mod.FullyParallelAttention.get_xqkv(me, x, y)
+    np.savez_compressed(os.path.join(out_dir, "xqkv.npz"), x=bf16_bits(x[:, 0]), y=bf16_bits(y), wqx=bf16_bits(lin.qx.weight),
+                        wkv=bf16_bits(kv_lin.weight), gq=qn.weight.detach().numpy(), bq=qn.bias.detach().numpy(),
+                        gk=kn.weight.detach().numpy(), bk=kn.bias.detach().numpy(), q=bf16_bits(q), k=bf16_bits(k), v=bf16_bits(v))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", required=True, help="root of the MAGI-1 checkout")
@@ -403,7 +432,7 @@ def main():
     a = ap.parse_args()
     sys.path.insert(0, a.ref)
     only = set(a.only.split(",")) if a.only else None
-    if only is None or only & {"prologue", "rope", "modulate", "div_clamp", "linear_prologue"}:
+    if only is None or only & {"prologue", "rope", "modulate", "div_clamp", "linear_prologue", "xqkv"}:
         import inference.model.dit.dit_module as ref_mod
         if only is None or "prologue" in only:
             gen_prologue(ref_mod, a.out)
@@ -415,6 +444,8 @@ def main():
             gen_div_clamp(ref_mod, a.out)
         if only is None or "linear_prologue" in only:
             gen_linear_prologue(ref_mod, a.out)
+        if only is None or "xqkv" in only:
+            gen_xqkv(ref_mod, a.out)
     if only is None or "attn" in only:
         gen_attn_cfg0(a.out)
     if only is None or "ulysses" in only:

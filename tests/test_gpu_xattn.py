@@ -50,6 +50,22 @@ def test_cross_attention_shape_and_norm_without_rope():
         assert torch.equal(o_r, out[offs[r]:offs[r + 1]])
 
 
+def test_get_xqkv_matches_the_reference_fixture(golden_dir):
+    """inference.get_xqkv against FullyParallelAttention.get_xqkv run on the CPU (tests/golden/xqkv.npz)."""
+    import os
+    import magi_b200 as mb
+    from magi_b200 import inference
+    z = np.load(os.path.join(golden_dir, "xqkv.npz"))
+    b16 = lambda a: torch.from_numpy(a.copy()).view(torch.bfloat16)
+    q, k, v = inference.get_xqkv(b16(z["x"]).cuda(), b16(z["y"]).cuda(), b16(z["wqx"]).cuda(), b16(z["wkv"]).cuda(),
+                                 torch.from_numpy(z["gq"]), torch.from_numpy(z["bq"]), torch.from_numpy(z["gk"]), torch.from_numpy(z["bk"]))
+    torch.cuda.synchronize()
+    assert mb.Context.get().status() == 0
+    assert_close(q, b16(z["q"]), max_abs=4e-2, min_cos=0.99999, what="query_xattn vs reference")
+    assert_close(k, b16(z["k"]), max_abs=4e-2, min_cos=0.99999, what="key_xattn vs reference")
+    assert_close(v, b16(z["v"]), max_abs=2 ** -5, min_cos=0.99999, what="value_xattn vs reference")
+
+
 def test_get_xqkv_from_hidden_and_caption_states():
     """get_xqkv (dit_module.py:1005-1021) from the projections on: qx + q_layernorm_xattn (no rotary) and the K|V-interleaved
     linear_kv_xattn + k_layernorm_xattn, each one kernel, then the caption cross-attention over them against the oracle."""

@@ -48,6 +48,20 @@ def test_linear_prologue_matches_reference_projection_and_get_q(golden_dir):
     assert (v.float() - ref.float()).abs().max() <= 2 ** -6
 
 
+def test_get_xqkv_matches_the_reference_method(golden_dir):
+    """FullyParallelAttention.get_xqkv itself (run on the CPU for the fixture) against the oracle's restatement; the
+    reference's bf16 Linear and the oracle's exactly rounded matmul may differ by one bf16 ulp before the norms."""
+    z = np.load(os.path.join(golden_dir, "xqkv.npz"))
+    q, k, v = O.get_xqkv(_bf16(z["x"]), _bf16(z["y"]), _bf16(z["wqx"]), _bf16(z["wkv"]), torch.from_numpy(z["gq"]),
+                         torch.from_numpy(z["bq"]), torch.from_numpy(z["gk"]), torch.from_numpy(z["bk"]))
+    for got, name in ((q, "q"), (k, "k"), (v, "v")):
+        ref = _bf16(z[name])
+        assert got.shape == ref.shape, name
+        assert (got.float() - ref.float()).abs().max() <= (2 ** -6 if name == "v" else 4e-2), name
+        assert (got.view(torch.int16) != ref.view(torch.int16)).float().mean() < 0.03, name
+        assert O.cosine(got, ref) > 0.99999, name
+
+
 def test_rope_table_matches_reference_builder(golden_dir):
     z = np.load(os.path.join(golden_dir, "rope.npz"))
     for name in ("a", "b", "c"):
