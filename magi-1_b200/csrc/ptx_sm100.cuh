@@ -58,36 +58,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
-// Same bounded wait, polling with test_wait (the thread is never parked): for a thread that does nothing but wait and
-// whose reaction time is on the critical path.
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                               long long limit_cycles = 1000000000LL) {
-  if (mbar_test_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  int n = 0;
-  while (!mbar_test_wait(bar, parity)) {
-    if ((++n & 63) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > limit_cycles) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
 // ---------------------------------------------------------------- CTA pairs (cluster of two)
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
